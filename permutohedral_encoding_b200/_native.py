@@ -1,0 +1,309 @@
+"""ctypes binding of ``libpermuto_b200.so`` (the C ABI in ``include/permuto_b200.h``) and the
+three objects the reference's autograd code talks to.
+
+The reference reaches its kernels through a pybind11 module exposing ``EncodingInput``,
+``EncodingFixedParams`` and ``EncodingWrapper`` (reference: src/PyBridge.cxx:13-45).  The same
+three names live here with the same constructor arguments and method names, implemented on
+top of the C ABI, so the autograd functions read like the reference's
+(src/pytorch_modules/funcs.py:8-72).  One deliberate difference: features and their gradients
+are ``[N, 2*(L+extra)]`` tensors already in the module's output order instead of
+``[L+extra, 2, N]``, which removes the three transposing copies the reference pays per step.
+
+There is no CPU implementation and no fallback: if the shared library is missing this module
+raises at import time with the command that builds it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libpermuto_b200.so")
+
+PERMUTO_OK = 0
+PERMUTO_ERR_INVALID_ARGUMENT = -1
+PERMUTO_ERR_UNSUPPORTED = -2
+PERMUTO_ERR_CUDA = -3
+PERMUTO_ZERO_OUTPUTS = 1
+PERMUTO_NO_AGGREGATE = 2
+
+EXPORTED_SYMBOLS = (
+    "permuto_abi_version", "permuto_last_error", "permuto_extra_levels", "permuto_scale_factor",
+    "permuto_forward", "permuto_backward", "permuto_double_backward", "permuto_debug_lattice",
+)
+
+
+class PermutoConfig(C.Structure):
+    _fields_ = [("pos_dim", C.c_int32), ("nr_feat_per_level", C.c_int32), ("nr_levels", C.c_int32),
+                ("capacity", C.c_int32), ("concat_points", C.c_int32), ("points_scaling", C.c_float)]
+
+
+class PermutoInputs(C.Structure):
+    _fields_ = [("nr_positions", C.c_int64), ("positions", C.c_void_p), ("pos_stride_n", C.c_int64),
+                ("pos_stride_d", C.c_int64), ("lattice_values", C.c_void_p), ("scale_factor", C.c_void_p),
+                ("random_shift", C.c_void_p), ("anneal_window", C.c_void_p)]
+
+
+def _load() -> C.CDLL:
+    if not os.path.isfile(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA extension has not been built. Build it with "
+            "`python -m permutohedral_encoding_b200.build` (needs nvcc; no GPU required). "
+            "There is no CPU fallback.")
+    lib = C.CDLL(LIB_PATH)
+    lib.permuto_abi_version.restype = C.c_int
+    lib.permuto_last_error.restype = C.c_char_p
+    lib.permuto_extra_levels.restype = C.c_int
+    lib.permuto_extra_levels.argtypes = [C.c_int32, C.c_int32]
+    lib.permuto_scale_factor.restype = C.c_int
+    lib.permuto_scale_factor.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+    cfgp, inp = C.POINTER(PermutoConfig), C.POINTER(PermutoInputs)
+    lib.permuto_forward.restype = C.c_int
+    lib.permuto_forward.argtypes = [cfgp, inp, C.c_void_p, C.c_void_p]
+    lib.permuto_backward.restype = C.c_int
+    lib.permuto_backward.argtypes = [cfgp, inp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                     C.c_uint32, C.c_void_p]
+    lib.permuto_double_backward.restype = C.c_int
+    lib.permuto_double_backward.argtypes = [cfgp, inp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_uint32, C.c_void_p]
+    lib.permuto_debug_lattice.restype = C.c_int
+    lib.permuto_debug_lattice.argtypes = [cfgp, inp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    if lib.permuto_abi_version() != 1:
+        raise ImportError(f"{LIB_PATH}: ABI version {lib.permuto_abi_version()} != 1; rebuild the extension")
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return (lib.permuto_last_error() or b"").decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    """Turn a C-ABI status into the exception the reference would have raised (its CHECK
+    macros and std::runtime_error both surface as RuntimeError in Python)."""
+    if status != PERMUTO_OK:
+        raise RuntimeError(last_error() or f"permuto_b200 error {status}")
+
+
+def scale_factor(sigmas, pos_dim: int) -> np.ndarray:
+    s = np.ascontiguousarray(np.asarray(sigmas, dtype=np.float64))
+    out = np.empty((s.shape[0], int(pos_dim)), dtype=np.float32)
+    check(lib.permuto_scale_factor(s.ctypes.data, s.shape[0], int(pos_dim), out.ctypes.data))
+    return out
+
+
+def extra_levels(pos_dim: int, concat_points: bool) -> int:
+    return int(lib.permuto_extra_levels(int(pos_dim), int(bool(concat_points))))
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+class EncodingInput:
+    """Per-call bundle (reference: include/permutohedral_encoding/Encoding.cuh:14-29)."""
+
+    def __init__(self, lattice_values, positions, anneal_window, require_lattice_values_grad,
+                 require_positions_grad):
+        self.m_lattice_values = lattice_values
+        self.m_positions_raw = positions
+        self.m_anneal_window = anneal_window
+        self.m_require_lattice_values_grad = bool(require_lattice_values_grad)
+        self.m_require_positions_grad = bool(require_positions_grad)
+
+
+class EncodingFixedParams:
+    """Fixed description of an encoding (reference: Encoding.cuh:31-70).  Holds the shift
+    tensor by handle, so loading a state dict into the module's parameter is seen by the
+    kernels; the scale factor is computed once on the host with the reference's rounding and
+    cached per device."""
+
+    def __init__(self, pos_dim, capacity, nr_levels, nr_feat_per_level, sigmas_list, random_shift_per_level,
+                 concat_points, points_scaling):
+        self.m_pos_dim = int(pos_dim)
+        self.m_capacity = int(capacity)
+        self.m_nr_levels = int(nr_levels)
+        self.m_nr_feat_per_level = int(nr_feat_per_level)
+        self.m_sigmas_list = [float(s) for s in np.asarray(sigmas_list, dtype=np.float64).reshape(-1)]
+        self.m_random_shift_per_level = random_shift_per_level
+        self.m_concat_points = bool(concat_points)
+        self.m_points_scaling = float(points_scaling)
+        if len(self.m_sigmas_list) != self.m_nr_levels:
+            raise RuntimeError(f"scale list has {len(self.m_sigmas_list)} entries for {self.m_nr_levels} levels")
+        if not (2 <= self.m_pos_dim <= 7):
+            raise RuntimeError("Encoding: pos_dim must be 2,3,4,5,6 or 7")
+        self.m_scale_factor_host = torch.from_numpy(scale_factor(self.m_sigmas_list, self.m_pos_dim))
+        self._scale_by_device = {}
+
+    def scale_factor_on(self, device) -> torch.Tensor:
+        device = torch.device(device)
+        t = self._scale_by_device.get(device)
+        if t is None:
+            t = self.m_scale_factor_host.to(device)
+            self._scale_by_device[device] = t
+        return t
+
+    def config(self) -> PermutoConfig:
+        return PermutoConfig(self.m_pos_dim, self.m_nr_feat_per_level, self.m_nr_levels, self.m_capacity,
+                             int(self.m_concat_points), self.m_points_scaling)
+
+
+class EncodingWrapper:
+    """Type-erased encoding (reference: Encoding.cuh:159-188; launchers src/Encoding.cu:54-334)."""
+
+    def __init__(self, pos_dim, nr_feat_per_level, fixed_params: EncodingFixedParams):
+        if int(pos_dim) not in (2, 3, 4, 5, 6, 7):
+            raise RuntimeError("Encoding: pos_dim must be 2,3,4,5,6 or 7")
+        if int(nr_feat_per_level) != 2:
+            raise RuntimeError(
+                "Encoding: nr_feat_per_level must be 2 since other values are not yet implemented")
+        self.fixed = fixed_params
+        self.aggregate_collisions = True
+
+    @staticmethod
+    def create(pos_dim, nr_feat_per_level, fixed_params) -> "EncodingWrapper":
+        return EncodingWrapper(pos_dim, nr_feat_per_level, fixed_params)
+
+    # -- validation mirroring src/Encoding.cu:37-45, :63-66, :119-125 ---------------------------
+    def _check(self, inp: EncodingInput):
+        fp = self.fixed
+        pos, lv, aw, shift = inp.m_positions_raw, inp.m_lattice_values, inp.m_anneal_window, fp.m_random_shift_per_level
+        if not pos.is_cuda:
+            raise RuntimeError("positions should be in GPU memory. Please call .cuda() on the tensor")
+        if pos.dtype != torch.float32:
+            raise RuntimeError("positions should be of type float")
+        if pos.dim() != 2:
+            raise RuntimeError(f"positions should have dim 2 correspondin to HW. However it has sizes {tuple(pos.shape)}")
+        if pos.shape[0] == 0:
+            raise RuntimeError("Why do we have 0 points")
+        if pos.shape[1] != fp.m_pos_dim:
+            raise RuntimeError("Pos dim for the lattice doesn't correspond with the position of the points. "
+                               f"Lattice was initialized with {fp.m_pos_dim} and points have pos dim {pos.shape[1]}")
+        if lv.dim() != 3 or tuple(lv.shape) != (fp.m_nr_levels, fp.m_capacity, 2):
+            raise RuntimeError(f"lattice_values should be nr_levels x capacity x 2, got {tuple(lv.shape)}")
+        if not lv.is_contiguous():
+            raise RuntimeError("We assume that the lattice_values_monolithic are contiguous because in the cuda "
+                               "code we make a load of 2 float values at a time")
+        if lv.dtype != torch.float32 or lv.device != pos.device:
+            raise RuntimeError("lattice_values should be float32 on the device of the positions")
+        if tuple(shift.shape) != (fp.m_nr_levels, fp.m_pos_dim):
+            raise RuntimeError("Random shift should be nr of resolutions x pos dim")
+        if aw.dim() != 1 or aw.shape[0] != fp.m_nr_levels:
+            raise RuntimeError("anneal_window should have the first dimension the same as the nr of resolutions")
+
+    def _inputs(self, inp: EncodingInput):
+        fp = self.fixed
+        pos = inp.m_positions_raw
+        dev = pos.device
+        shift = fp.m_random_shift_per_level
+        if shift.device != dev or shift.dtype != torch.float32 or not shift.is_contiguous():
+            shift = shift.detach().to(device=dev, dtype=torch.float32).contiguous()
+        aw = inp.m_anneal_window
+        if aw.device != dev or aw.dtype != torch.float32 or not aw.is_contiguous():
+            aw = aw.detach().to(device=dev, dtype=torch.float32).contiguous()
+        scale = fp.scale_factor_on(dev)
+        keep = (shift, aw, scale)
+        ins = PermutoInputs(pos.shape[0], pos.data_ptr(), pos.stride(0), pos.stride(1),
+                            inp.m_lattice_values.data_ptr(), scale.data_ptr(), shift.data_ptr(), aw.data_ptr())
+        return ins, keep
+
+    def output_width(self) -> int:
+        fp = self.fixed
+        return 2 * (fp.m_nr_levels + extra_levels(fp.m_pos_dim, fp.m_concat_points))
+
+    def _flags(self, zero=True) -> int:
+        f = PERMUTO_ZERO_OUTPUTS if zero else 0
+        if not self.aggregate_collisions:
+            f |= PERMUTO_NO_AGGREGATE
+        return f
+
+    # -- the three operations -------------------------------------------------------------------
+    def forward(self, inp: EncodingInput) -> torch.Tensor:
+        """features [N, 2*(L+extra)] (reference: Encoding<P,2>::forward + modules.py:87)."""
+        self._check(inp)
+        pos = inp.m_positions_raw
+        cfg = self.fixed.config()
+        out = torch.empty((pos.shape[0], self.output_width()), dtype=torch.float32, device=pos.device)
+        with torch.cuda.device(pos.device):
+            ins, keep = self._inputs(inp)
+            check(lib.permuto_forward(C.byref(cfg), C.byref(ins), _ptr(out), _stream(pos.device)))
+        return out
+
+    def backward(self, inp: EncodingInput, grad_features: torch.Tensor, lattice_grad_out=None,
+                 level_begin=None, level_end=None, zero=True):
+        """(lattice_values_grad [L,C,2] | None, positions_grad [N,d] | None)
+        (reference: Encoding<P,2>::backward).  ``lattice_grad_out`` lets the caller provide the
+        buffer; ``level_begin/level_end`` restrict the levels (bucketed all-reduce overlap)."""
+        self._check(inp)
+        fp = self.fixed
+        pos = inp.m_positions_raw
+        n = pos.shape[0]
+        if grad_features.dim() != 2 or tuple(grad_features.shape) != (n, self.output_width()):
+            raise RuntimeError("The nr of positions should match between the input positions and the sliced values: "
+                               f"expected {(n, self.output_width())}, got {tuple(grad_features.shape)}")
+        if not grad_features.is_contiguous():
+            raise RuntimeError("Grad sliced values needs to be contiguous. Please call .contiguous() on it")
+        cfg = fp.config()
+        lv_grad = None
+        if inp.m_require_lattice_values_grad:
+            lv_grad = lattice_grad_out if lattice_grad_out is not None else torch.empty_like(inp.m_lattice_values)
+        pos_grad = torch.empty((n, fp.m_pos_dim), dtype=torch.float32, device=pos.device) \
+            if inp.m_require_positions_grad else None
+        lb = 0 if level_begin is None else int(level_begin)
+        le = fp.m_nr_levels if level_end is None else int(level_end)
+        with torch.cuda.device(pos.device):
+            ins, keep = self._inputs(inp)
+            check(lib.permuto_backward(C.byref(cfg), C.byref(ins), _ptr(grad_features), _ptr(lv_grad), _ptr(pos_grad),
+                                       lb, le, self._flags(zero), _stream(pos.device)))
+        return lv_grad, pos_grad
+
+    def double_backward_from_positions(self, inp: EncodingInput, double_positions_grad: torch.Tensor,
+                                       grad_features: torch.Tensor, need_lattice_grad=True,
+                                       need_grad_grad_features=True):
+        """(lattice_values_grad [L,C,2], grad_grad_features [N,W])
+        (reference: Encoding<P,2>::double_backward_from_positions)."""
+        self._check(inp)
+        fp = self.fixed
+        pos = inp.m_positions_raw
+        n = pos.shape[0]
+        if tuple(double_positions_grad.shape) != (n, fp.m_pos_dim):
+            raise RuntimeError("double_positions_grad should be nr_positions x pos_dim")
+        if tuple(grad_features.shape) != (n, self.output_width()):
+            raise RuntimeError("The nr of positions should match between the input positions and the sliced values")
+        dpg = double_positions_grad.contiguous()
+        gf = grad_features.contiguous()
+        cfg = fp.config()
+        lv_grad = torch.empty_like(inp.m_lattice_values) if need_lattice_grad else None
+        ggf = torch.empty_like(gf) if need_grad_grad_features else None
+        with torch.cuda.device(pos.device):
+            ins, keep = self._inputs(inp)
+            check(lib.permuto_double_backward(C.byref(cfg), C.byref(ins), _ptr(dpg), _ptr(gf), _ptr(lv_grad),
+                                              _ptr(ggf), self._flags(True), _stream(pos.device)))
+        return lv_grad, ggf
+
+    def debug_lattice(self, inp: EncodingInput, want=("keys", "slots", "bary", "rank")):
+        """Lattice keys / hash slots / barycentric weights / ranks per (point, level, vertex)."""
+        self._check(inp)
+        fp = self.fixed
+        pos = inp.m_positions_raw
+        n, d, nl = pos.shape[0], fp.m_pos_dim, fp.m_nr_levels
+        dev = pos.device
+        keys = torch.empty((n, nl, d + 1, d), dtype=torch.int32, device=dev) if "keys" in want else None
+        slots = torch.empty((n, nl, d + 1), dtype=torch.int32, device=dev) if "slots" in want else None
+        bary = torch.empty((n, nl, d + 1), dtype=torch.float32, device=dev) if "bary" in want else None
+        rank = torch.empty((n, nl, d + 1), dtype=torch.int32, device=dev) if "rank" in want else None
+        cfg = fp.config()
+        with torch.cuda.device(dev):
+            ins, keep = self._inputs(inp)
+            check(lib.permuto_debug_lattice(C.byref(cfg), C.byref(ins), _ptr(keys), _ptr(slots), _ptr(bary),
+                                            _ptr(rank), _stream(dev)))
+        return {"keys": keys, "slots": slots, "bary": bary, "rank": rank}

@@ -1,0 +1,474 @@
+// Lattice kernels for one pos_dim (compile with -DPERMUTO_DIM=2..7), sm_100a.
+//
+// Work decomposition shared by all kernels: one thread owns one point and LPT consecutive
+// levels.  blockIdx.x walks point tiles, blockIdx.y walks level groups, and blocks are
+// dispatched x-fastest, so the whole grid sweeps the points once per level group: the
+// slices of the value table (and of its gradient) that are live at any time are the LPT
+// slices of one group, which stay L2-resident.  With LPT = 4 and two features per level a
+// thread produces / consumes 8 consecutive floats of a feature row = one 32-byte sector,
+// moved with a single 256-bit access (ld/st.global.v8.f32, new on sm_100), directly in the
+// final [N, 2L] layout -- no transposed intermediate.
+//
+// What each kernel replaces in the reference (paths relative to its root):
+//   forward_kernel          kernels/permutohedral_encoding/EncodingGPU.cuh:68-256
+//   backward_kernel         EncodingGPU.cuh:259-414 (table) and :530-769 (positions), fused
+//   double_backward_kernel  EncodingGPU.cuh:1016-1257 and :1260-1493, fused
+#include "permuto_geometry.cuh"
+#include "permuto_internal.h"
+
+#ifndef PERMUTO_DIM
+#error "compile with -DPERMUTO_DIM=<2..7>"
+#endif
+
+namespace permuto {
+namespace {
+
+constexpr int D = PERMUTO_DIM;
+constexpr int kThreads = 256;
+constexpr unsigned kFullMask = 0xffffffffu;
+
+__device__ __forceinline__ void load_pos(const Problem& p, int64_t n, float (&pos)[D]) {
+    const float* src = p.positions + n * p.pos_stride_n;
+#pragma unroll
+    for (int i = 0; i < D; ++i) pos[i] = __ldg(src + i * p.pos_stride_d);
+}
+
+__device__ __forceinline__ uint32_t to_slot(const Problem& p, uint32_t h) {
+    return p.cap_is_pow2 ? (h & (p.capacity - 1u)) : (h % p.capacity);
+}
+
+// 8 consecutive floats of a feature row, 32-byte aligned
+__device__ __forceinline__ void load8(const float* src, float (&v)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+                 : "l"(src));
+}
+__device__ __forceinline__ void store8(float* dst, const float (&v)[8]) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "f"(v[0]), "f"(v[1]),
+                 "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                 : "memory");
+}
+
+// Row segment [2*l0, 2*(l0+LPT)) of point n: vector path when the whole group is inside the
+// level range and rows are 32-byte aligned, else per-level float2 accesses.
+template <int LPT>
+__device__ __forceinline__ void load_row_segment(const Problem& p, const float* rows, int64_t n, int l0,
+                                                 float (&v)[2 * LPT]) {
+    const float* src = rows + n * p.width + 2 * l0;
+    if (LPT == 4 && p.rows_vec8_ok && l0 + LPT <= p.level_end) {
+        float t[8];
+        load8(src, t);
+#pragma unroll
+        for (int i = 0; i < 2 * LPT; ++i) v[i] = t[i % 8];
+    } else {
+#pragma unroll
+        for (int k = 0; k < LPT; ++k) {
+            float2 g = make_float2(0.f, 0.f);
+            if (l0 + k < p.level_end) g = __ldg(reinterpret_cast<const float2*>(src) + k);
+            v[2 * k] = g.x;
+            v[2 * k + 1] = g.y;
+        }
+    }
+}
+template <int LPT>
+__device__ __forceinline__ void store_row_segment(const Problem& p, float* rows, int64_t n, int l0,
+                                                  const float (&v)[2 * LPT]) {
+    float* dst = rows + n * p.width + 2 * l0;
+    if (LPT == 4 && p.rows_vec8_ok && l0 + LPT <= p.level_end) {
+        float t[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = v[i % (2 * LPT)];
+        store8(dst, t);
+    } else {
+#pragma unroll
+        for (int k = 0; k < LPT; ++k)
+            if (l0 + k < p.level_end) reinterpret_cast<float2*>(dst)[k] = make_float2(v[2 * k], v[2 * k + 1]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// forward
+// ------------------------------------------------------------------------------------------
+template <int LPT>
+__global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardArgs a) {
+    const Problem& p = a.p;
+    const int64_t n = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (n >= p.n_points) return;
+    const int l0 = p.level_begin + (int)blockIdx.y * LPT;
+
+    float pos[D];
+    load_pos(p, n, pos);
+
+    float out[2 * LPT];
+#pragma unroll
+    for (int k = 0; k < LPT; ++k) {
+        const int l = l0 + k;
+        float ax = 0.f, ay = 0.f;
+        if (l < p.level_end) {  // uniform over the block
+            const float w_lvl = __ldg(p.anneal + l);
+            if (w_lvl != 0.0f) {  // a closed coarse-to-fine window contributes exact zeros
+                Simplex<D> s;
+                locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+                uint32_t h[D + 1];
+                vertex_hashes<D>(s, h);
+                const float* base = p.table + (size_t)l * p.capacity * 2u;
+                float2 v[D + 1];
+#pragma unroll
+                for (int r = 0; r <= D; ++r) v[r] = gather2(base, to_slot(p, h[r]));
+#pragma unroll
+                for (int r = 0; r <= D; ++r) {
+                    const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:234
+                    ax = fmaf(v[r].x, w, ax);
+                    ay = fmaf(v[r].y, w, ay);
+                }
+            }
+        }
+        out[2 * k] = ax;
+        out[2 * k + 1] = ay;
+    }
+    store_row_segment<LPT>(p, a.features, n, l0, out);
+
+    // raw points appended after the lattice levels (EncodingGPU.cuh:105-121)
+    if (p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {
+        float* dst = a.features + n * p.width + 2 * p.nr_levels;
+        for (int c = 0; c < 2 * p.extra_levels; ++c) {
+            float v = 0.f;
+#pragma unroll
+            for (int i = 0; i < D; ++i) v = (c == i) ? pos[i] * p.points_scaling : v;
+            dst[c] = v;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// scatter-add of one table-gradient entry per lane, colliding lanes merged first
+// ------------------------------------------------------------------------------------------
+// On coarse levels the 32 points of a warp hit a handful of slots; sending 32 same-address
+// reductions to L2 serialises there.  match.any groups the lanes by slot, a pointer-jumping
+// suffix sum over each group's lanes (log2 of the largest group rounds) leaves the group total
+// in its lowest lane, and only that lane issues the vector reduction.  The summation order is
+// fixed by the lane order, so a warp's contribution is deterministic.
+__device__ __forceinline__ void scatter_merged(float* level_base, uint32_t slot, float x, float y, bool active,
+                                               unsigned lane) {
+    const uint32_t key = active ? slot : (0xffffffffu - lane);  // idle lanes match nobody
+    const unsigned group = __match_any_sync(kFullMask, key);
+    const int largest = __reduce_max_sync(kFullMask, __popc(group));
+    if (largest > 1) {  // warp-uniform
+        const unsigned above = group & (0xfffffffeu << lane);
+        int next = above ? (__ffs(above) - 1) : -1;
+        for (int span = 1; span < largest; span <<= 1) {
+            const int src = next >= 0 ? next : (int)lane;
+            const float x2 = __shfl_sync(kFullMask, x, src);
+            const float y2 = __shfl_sync(kFullMask, y, src);
+            const int n2 = __shfl_sync(kFullMask, next, src);
+            if (next >= 0) {
+                x += x2;
+                y += y2;
+                next = n2;
+            }
+        }
+        const bool leader = (group & ((1u << lane) - 1u)) == 0u;
+        if (leader && active) red_add2(level_base, slot, x, y);
+    } else if (active) {
+        red_add2(level_base, slot, x, y);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// first-order backward: table gradient (scatter) and/or position gradient (gather)
+// ------------------------------------------------------------------------------------------
+template <int LPT, bool TABLE, bool POS>
+__global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a) {
+    const Problem& p = a.p;
+    const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const bool active = n_raw < p.n_points;
+    const int64_t n = active ? n_raw : p.n_points - 1;  // idle lanes shadow the last point
+    const int l0 = p.level_begin + (int)blockIdx.y * LPT;
+    const unsigned lane = threadIdx.x & 31u;
+    constexpr float kInv = 1.0f / (D + 1);
+
+    float pos[D];
+    load_pos(p, n, pos);
+    float g[2 * LPT];
+    load_row_segment<LPT>(p, a.grad_features, n, l0, g);
+
+    float dpos[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) dpos[i] = 0.f;
+
+#pragma unroll
+    for (int k = 0; k < LPT; ++k) {
+        const int l = l0 + k;
+        if (l >= p.level_end) continue;  // uniform
+        const float w_lvl = __ldg(p.anneal + l);
+        if (w_lvl == 0.0f) continue;  // every addend of this level is an exact zero
+        Simplex<D> s;
+        locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+        uint32_t h[D + 1];
+        vertex_hashes<D>(s, h);
+        uint32_t slot[D + 1];
+#pragma unroll
+        for (int r = 0; r <= D; ++r) slot[r] = to_slot(p, h[r]);
+        const float gx = g[2 * k], gy = g[2 * k + 1];
+
+        if (POS) {
+            // EncodingGPU.cuh:671-749
+            const float* base = p.table + (size_t)l * p.capacity * 2u;
+            float dBs[D + 2];
+#pragma unroll
+            for (int r = 0; r <= D; ++r) {
+                const float2 v = gather2(base, slot[r]);
+                float t = v.x * w_lvl * gx;
+                t += v.y * w_lvl * gy;
+                dBs[r] = t * kInv;
+            }
+            dBs[D + 1] = dBs[0];
+            float T[D + 1];  // dE of the coordinate whose rank is k
+#pragma unroll
+            for (int kk = 0; kk <= D; ++kk) T[kk] = dBs[D - kk] - dBs[D + 1 - kk];
+            float dE[D + 1];
+#pragma unroll
+            for (int i = 0; i <= D; ++i) {
+                float v = 0.f;
+#pragma unroll
+                for (int kk = 0; kk <= D; ++kk) v = (s.rank[i] == kk) ? T[kk] : v;
+                dE[i] = v;
+            }
+            float run = 0.f;
+#pragma unroll
+            for (int i = 0; i < D; ++i) {
+                run += dE[i];
+                const float sc = __ldg(p.scale + l * D + i);
+                dpos[i] += sc * (run - (float)(i + 1) * dE[i + 1]);
+            }
+        }
+
+        if (TABLE) {
+            float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
+            bool merge = false;
+            if (a.aggregate) {
+                // probe with vertex 0: if no two lanes share its slot the level is fine-grained
+                const uint32_t key = active ? slot[0] : (0xffffffffu - lane);
+                const unsigned grp = __match_any_sync(kFullMask, key);
+                merge = __reduce_max_sync(kFullMask, __popc(grp)) > 1;
+            }
+#pragma unroll
+            for (int r = 0; r <= D; ++r) {
+                const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:405-410
+                const float ax = gx * w, ay = gy * w;
+                if (merge) {
+                    scatter_merged(gbase, slot[r], ax, ay, active, lane);
+                } else if (active) {
+                    red_add2(gbase, slot[r], ax, ay);
+                }
+            }
+        }
+    }
+    if (POS && active) {
+        float* dst = a.positions_grad + n * D;
+#pragma unroll
+        for (int i = 0; i < D; ++i) red_add1(dst + i, dpos[i]);  // accumulates across level groups
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// double backward of the position gradient
+// ------------------------------------------------------------------------------------------
+template <int LPT, bool TABLE, bool GGF>
+__global__ void __launch_bounds__(kThreads) double_backward_kernel(const DoubleBackwardArgs a) {
+    const Problem& p = a.p;
+    const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const bool active = n_raw < p.n_points;
+    const int64_t n = active ? n_raw : p.n_points - 1;
+    const int l0 = p.level_begin + (int)blockIdx.y * LPT;
+    const unsigned lane = threadIdx.x & 31u;
+    constexpr float kInv = 1.0f / (D + 1);
+
+    float pos[D], dpg[D];
+    load_pos(p, n, pos);
+#pragma unroll
+    for (int i = 0; i < D; ++i) dpg[i] = __ldg(a.double_positions_grad + n * D + i);
+    float g[2 * LPT];
+    if (TABLE) load_row_segment<LPT>(p, a.grad_features, n, l0, g);
+    float out[2 * LPT];
+
+#pragma unroll
+    for (int k = 0; k < LPT; ++k) {
+        const int l = l0 + k;
+        float ox = 0.f, oy = 0.f;
+        if (l < p.level_end) {
+            const float w_lvl = __ldg(p.anneal + l);
+            if (w_lvl != 0.0f) {
+                Simplex<D> s;
+                locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+                uint32_t h[D + 1];
+                vertex_hashes<D>(s, h);
+                uint32_t slot[D + 1];
+#pragma unroll
+                for (int r = 0; r <= D; ++r) slot[r] = to_slot(p, h[r]);
+
+                // d loss / d elevated (EncodingGPU.cuh:1187-1199)
+                float gs[D], dE[D + 1];
+#pragma unroll
+                for (int i = 0; i < D; ++i) gs[i] = dpg[i] * __ldg(p.scale + l * D + i);
+#pragma unroll
+                for (int j = 0; j <= D; ++j) dE[j] = 0.f;
+#pragma unroll
+                for (int i = 0; i < D; ++i) {
+#pragma unroll
+                    for (int j = 0; j <= i; ++j) dE[j] += gs[i];
+                }
+#pragma unroll
+                for (int i = 0; i < D; ++i) dE[i + 1] -= gs[i] * (float)(i + 1);
+                // d loss / d barycentric (EncodingGPU.cuh:1213-1218), via the rank-sorted vector
+                float sdE[D + 1];
+#pragma unroll
+                for (int kk = 0; kk <= D; ++kk) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int i = 0; i <= D; ++i) v = (s.rank[i] == kk) ? dE[i] * kInv : v;
+                    sdE[kk] = v;
+                }
+                float dB[D + 1];
+#pragma unroll
+                for (int m = 1; m <= D; ++m) dB[m] = sdE[D - m] - sdE[D + 1 - m];
+                dB[0] = sdE[D] - sdE[0];
+
+                if (GGF) {
+                    const float* base = p.table + (size_t)l * p.capacity * 2u;
+#pragma unroll
+                    for (int r = 0; r <= D; ++r) {
+                        const float2 v = gather2(base, slot[r]);
+                        const float c = dB[r] * w_lvl;  // EncodingGPU.cuh:1484-1485
+                        ox = fmaf(c, v.x, ox);
+                        oy = fmaf(c, v.y, oy);
+                    }
+                }
+                if (TABLE) {
+                    float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
+                    const float gx = g[2 * k], gy = g[2 * k + 1];
+                    bool merge = false;
+                    if (a.aggregate) {
+                        const uint32_t key = active ? slot[0] : (0xffffffffu - lane);
+                        const unsigned grp = __match_any_sync(kFullMask, key);
+                        merge = __reduce_max_sync(kFullMask, __popc(grp)) > 1;
+                    }
+#pragma unroll
+                    for (int r = 0; r <= D; ++r) {
+                        const float c = dB[r] * w_lvl;  // EncodingGPU.cuh:1244-1245
+                        const float ax = c * gx, ay = c * gy;
+                        if (merge) {
+                            scatter_merged(gbase, slot[r], ax, ay, active, lane);
+                        } else if (active) {
+                            red_add2(gbase, slot[r], ax, ay);
+                        }
+                    }
+                }
+            }
+        }
+        out[2 * k] = ox;
+        out[2 * k + 1] = oy;
+    }
+    if (GGF && active) {
+        store_row_segment<LPT>(p, a.grad_grad_features, n, l0, out);
+        if (p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {  // EncodingGPU.cuh:1290-1295
+            float* dst = a.grad_grad_features + n * p.width + 2 * p.nr_levels;
+            for (int c = 0; c < 2 * p.extra_levels; ++c) dst[c] = 0.f;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// debug view: one thread per (point, level)
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) debug_kernel(const DebugArgs a) {
+    const Problem& p = a.p;
+    const int64_t n = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (n >= p.n_points) return;
+    const int l = blockIdx.y;
+    float pos[D];
+    load_pos(p, n, pos);
+    Simplex<D> s;
+    locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+    uint32_t h[D + 1];
+    vertex_hashes<D>(s, h);
+    const int64_t base = (n * p.nr_levels + l) * (D + 1);
+#pragma unroll
+    for (int r = 0; r <= D; ++r) {
+        if (a.keys) {
+            int key[D];
+            vertex_key<D>(s, r, key);
+#pragma unroll
+            for (int i = 0; i < D; ++i) a.keys[(base + r) * D + i] = key[i];
+        }
+        if (a.slots) a.slots[base + r] = (int32_t)to_slot(p, h[r]);
+        if (a.bary) a.bary[base + r] = s.bary[r];
+        if (a.rank) a.rank[base + r] = s.rank[r];
+    }
+}
+
+inline dim3 grid_for(const Problem& p, int lpt) {
+    const unsigned gx = (unsigned)((p.n_points + kThreads - 1) / kThreads);
+    const unsigned gy = (unsigned)((p.level_end - p.level_begin + lpt - 1) / lpt);
+    return dim3(gx, gy, 1);
+}
+
+// small problems get one level per thread so that the grid still covers the machine
+inline bool use_single_level(const Problem& p) {
+    const int64_t groups4 = (p.level_end - p.level_begin + 3) / 4;
+    const int64_t blocks4 = ((p.n_points + kThreads - 1) / kThreads) * groups4;
+    return blocks4 < 2 * 148;
+}
+
+}  // namespace
+
+#define PERMUTO_CAT_(a, b) a##b
+#define PERMUTO_CAT(a, b) PERMUTO_CAT_(a, b)
+
+cudaError_t PERMUTO_CAT(launch_forward_dim, PERMUTO_DIM)(const ForwardArgs& a, cudaStream_t st) {
+    if (use_single_level(a.p))
+        forward_kernel<1><<<grid_for(a.p, 1), kThreads, 0, st>>>(a);
+    else
+        forward_kernel<4><<<grid_for(a.p, 4), kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+template <int LPT>
+static cudaError_t launch_backward_lpt(const BackwardArgs& a, cudaStream_t st) {
+    const dim3 g = grid_for(a.p, LPT);
+    if (a.lattice_grad && a.positions_grad)
+        backward_kernel<LPT, true, true><<<g, kThreads, 0, st>>>(a);
+    else if (a.lattice_grad)
+        backward_kernel<LPT, true, false><<<g, kThreads, 0, st>>>(a);
+    else if (a.positions_grad)
+        backward_kernel<LPT, false, true><<<g, kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t PERMUTO_CAT(launch_backward_dim, PERMUTO_DIM)(const BackwardArgs& a, cudaStream_t st) {
+    return use_single_level(a.p) ? launch_backward_lpt<1>(a, st) : launch_backward_lpt<4>(a, st);
+}
+
+template <int LPT>
+static cudaError_t launch_double_lpt(const DoubleBackwardArgs& a, cudaStream_t st) {
+    const dim3 g = grid_for(a.p, LPT);
+    if (a.lattice_grad && a.grad_grad_features)
+        double_backward_kernel<LPT, true, true><<<g, kThreads, 0, st>>>(a);
+    else if (a.lattice_grad)
+        double_backward_kernel<LPT, true, false><<<g, kThreads, 0, st>>>(a);
+    else if (a.grad_grad_features)
+        double_backward_kernel<LPT, false, true><<<g, kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t PERMUTO_CAT(launch_double_backward_dim, PERMUTO_DIM)(const DoubleBackwardArgs& a, cudaStream_t st) {
+    return use_single_level(a.p) ? launch_double_lpt<1>(a, st) : launch_double_lpt<4>(a, st);
+}
+
+cudaError_t PERMUTO_CAT(launch_debug_dim, PERMUTO_DIM)(const DebugArgs& a, cudaStream_t st) {
+    const dim3 g((unsigned)((a.p.n_points + kThreads - 1) / kThreads), (unsigned)a.p.nr_levels, 1);
+    debug_kernel<<<g, kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace permuto

@@ -1,0 +1,74 @@
+// Internal launch interface between the C-ABI translation unit and the per-dimension kernel
+// translation units (one object file per pos_dim so that they compile in parallel).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace permuto {
+
+// Everything a kernel needs to walk the lattice for a range of levels.
+struct Problem {
+    const float* positions;
+    int64_t pos_stride_n;
+    int64_t pos_stride_d;
+    const float* table;   // [L, C, 2]
+    const float* scale;   // [L, D]
+    const float* shift;   // [L, D]
+    const float* anneal;  // [L]
+    int64_t n_points;
+    int32_t nr_levels;
+    uint32_t capacity;
+    int32_t cap_is_pow2;
+    int32_t width;        // 2 * (L + extra): row length of features / gradients
+    int32_t level_begin;  // levels [level_begin, level_end) are processed
+    int32_t level_end;
+    int32_t extra_levels; // concat rows
+    float points_scaling;
+    int32_t rows_vec8_ok; // feature rows may be moved with 32-byte vector accesses
+};
+
+struct ForwardArgs {
+    Problem p;
+    float* features;
+};
+
+struct BackwardArgs {
+    Problem p;
+    const float* grad_features;
+    float* lattice_grad;    // may be null
+    float* positions_grad;  // may be null
+    int32_t aggregate;      // merge colliding scatter-adds inside a warp
+};
+
+struct DoubleBackwardArgs {
+    Problem p;
+    const float* double_positions_grad;
+    const float* grad_features;
+    float* lattice_grad;        // may be null
+    float* grad_grad_features;  // may be null
+    int32_t aggregate;
+};
+
+struct DebugArgs {
+    Problem p;
+    int32_t* keys;
+    int32_t* slots;
+    float* bary;
+    int32_t* rank;
+};
+
+// Defined once per pos_dim in permuto_dim.cu (compiled with -DPERMUTO_DIM=d).
+#define PERMUTO_DECLARE_DIM(d)                                                        \
+    cudaError_t launch_forward_dim##d(const ForwardArgs&, cudaStream_t);              \
+    cudaError_t launch_backward_dim##d(const BackwardArgs&, cudaStream_t);            \
+    cudaError_t launch_double_backward_dim##d(const DoubleBackwardArgs&, cudaStream_t); \
+    cudaError_t launch_debug_dim##d(const DebugArgs&, cudaStream_t);
+PERMUTO_DECLARE_DIM(2)
+PERMUTO_DECLARE_DIM(3)
+PERMUTO_DECLARE_DIM(4)
+PERMUTO_DECLARE_DIM(5)
+PERMUTO_DECLARE_DIM(6)
+PERMUTO_DECLARE_DIM(7)
+#undef PERMUTO_DECLARE_DIM
+
+}  // namespace permuto
