@@ -69,8 +69,9 @@ typedef struct permuto_inputs {
 
 /* Flags of permuto_backward / permuto_double_backward. */
 enum {
-    PERMUTO_ZERO_OUTPUTS = 1, /* clear lattice_grad (the selected levels) and positions_grad before accumulating */
-    PERMUTO_NO_AGGREGATE = 2  /* do not merge colliding scatter-adds inside a warp before the atomics            */
+    PERMUTO_ZERO_OUTPUTS = 1,      /* clear lattice_grad (the selected levels) and positions_grad before accumulating */
+    PERMUTO_NO_AGGREGATE = 2,      /* do not merge colliding scatter-adds inside a warp before the atomics            */
+    PERMUTO_KEEP_POSITIONS_GRAD = 4 /* with ZERO_OUTPUTS: leave positions_grad as it is (a later bucket of levels)     */
 };
 
 int permuto_abi_version(void);

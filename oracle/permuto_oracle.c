@@ -27,7 +27,17 @@
 #define PERMUTO_MAX_DIM 7
 #define NFEAT 2
 
-/* 1 = elevated[i] = fma(-i, cf, sm) (nvcc default contraction), 0 = separate mul and sub. */
+/* How nvcc's default -fmad=true contracts the reference's elevate loop
+ * (EncodingGPU.cuh:130-138; cf_i = t_i*scale_i with t_i = pos_i + shift_i).  Determined by
+ * exhaustive search over the legal contractions against the reference's outputs on a B200
+ * (tests/golden/, every pos_dim 2..7 reproduces with zero mismatches under exactly this rule):
+ *   i = d      : elevated[d] = -(d*cf_d), sm = cf_d                      (sm starts at 0)
+ *   2 <= i < d : elevated[i] = fma(-i, cf_i, sm), sm = sm + cf_i         (cf_i stays a rounded product:
+ *                                                                          it feeds i*cf_i)
+ *   i = 1      : elevated[1] = fma(-t_1, scale_1, sm), elevated[0] = fma(t_1, scale_1, sm)
+ *                                                                         (1*cf folds away, so both uses
+ *                                                                          of the product fuse)
+ * 1 = that rule (default), 0 = no contraction anywhere (kept to show the fixtures tell them apart). */
 static int g_fma_elevate = 1;
 /* 1 = scale = fl(base) * fl(1/sigma) (ATen tensor/scalar division multiplies by the
  * reciprocal), 0 = fl(base) / sigma. */
@@ -88,14 +98,24 @@ static void locate_simplex(int d, const float *pos, const float *shift, const fl
     const float inv = 1.0f / (float)(d + 1);
     float sm = 0.0f;
     for (int i = d; i > 0; i--) {
-        float cf = (pos[i - 1] + shift[i - 1]) * scale[i - 1];
-        if (g_fma_elevate) {
-            s->elevated[i] = fmaf(-(float)i, cf, sm);
+        float t = pos[i - 1] + shift[i - 1];
+        float sc = scale[i - 1];
+        float cf = t * sc;
+        if (!g_fma_elevate) {
+            float icf = (float)i * cf;
+            s->elevated[i] = sm - icf;
+            sm = sm + cf;
+        } else if (i == 1) {
+            s->elevated[i] = fmaf(-t, sc, sm);
+            sm = fmaf(t, sc, sm);
+        } else if (i == d) {
+            float icf = (float)i * cf;
+            s->elevated[i] = -icf;
+            sm = cf;
         } else {
-            float t = (float)i * cf;
-            s->elevated[i] = sm - t;
+            s->elevated[i] = fmaf(-(float)i, cf, sm);
+            sm = sm + cf;
         }
-        sm += cf;
     }
     s->elevated[0] = sm;
 

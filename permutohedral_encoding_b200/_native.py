@@ -29,6 +29,7 @@ PERMUTO_ERR_UNSUPPORTED = -2
 PERMUTO_ERR_CUDA = -3
 PERMUTO_ZERO_OUTPUTS = 1
 PERMUTO_NO_AGGREGATE = 2
+PERMUTO_KEEP_POSITIONS_GRAD = 4
 
 EXPORTED_SYMBOLS = (
     "permuto_abi_version", "permuto_last_error", "permuto_extra_levels", "permuto_scale_factor",
@@ -239,10 +240,11 @@ class EncodingWrapper:
         return out
 
     def backward(self, inp: EncodingInput, grad_features: torch.Tensor, lattice_grad_out=None,
-                 level_begin=None, level_end=None, zero=True):
+                 level_begin=None, level_end=None, zero=True, positions_grad_out=None):
         """(lattice_values_grad [L,C,2] | None, positions_grad [N,d] | None)
         (reference: Encoding<P,2>::backward).  ``lattice_grad_out`` lets the caller provide the
-        buffer; ``level_begin/level_end`` restrict the levels (bucketed all-reduce overlap)."""
+        buffer; ``level_begin/level_end`` restrict the levels (bucketed all-reduce overlap);
+        ``positions_grad_out`` is an existing position gradient to keep accumulating into."""
         self._check(inp)
         fp = self.fixed
         pos = inp.m_positions_raw
@@ -256,14 +258,20 @@ class EncodingWrapper:
         lv_grad = None
         if inp.m_require_lattice_values_grad:
             lv_grad = lattice_grad_out if lattice_grad_out is not None else torch.empty_like(inp.m_lattice_values)
-        pos_grad = torch.empty((n, fp.m_pos_dim), dtype=torch.float32, device=pos.device) \
-            if inp.m_require_positions_grad else None
+        pos_grad = None
+        flags = self._flags(zero)
+        if inp.m_require_positions_grad:
+            if positions_grad_out is not None:
+                pos_grad = positions_grad_out
+                flags |= PERMUTO_KEEP_POSITIONS_GRAD
+            else:
+                pos_grad = torch.empty((n, fp.m_pos_dim), dtype=torch.float32, device=pos.device)
         lb = 0 if level_begin is None else int(level_begin)
         le = fp.m_nr_levels if level_end is None else int(level_end)
         with torch.cuda.device(pos.device):
             ins, keep = self._inputs(inp)
             check(lib.permuto_backward(C.byref(cfg), C.byref(ins), _ptr(grad_features), _ptr(lv_grad), _ptr(pos_grad),
-                                       lb, le, self._flags(zero), _stream(pos.device)))
+                                       lb, le, flags, _stream(pos.device)))
         return lv_grad, pos_grad
 
     def double_backward_from_positions(self, inp: EncodingInput, double_positions_grad: torch.Tensor,

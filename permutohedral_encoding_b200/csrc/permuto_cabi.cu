@@ -157,7 +157,7 @@ int permuto_backward(const permuto_config* cfg, const permuto_inputs* in, const 
         if (lattice_grad && level_end > level_begin)
             e = cudaMemsetAsync(lattice_grad + (size_t)level_begin * a.p.capacity * 2u, 0,
                                 (size_t)(level_end - level_begin) * a.p.capacity * 2u * sizeof(float), st);
-        if (e == cudaSuccess && positions_grad)
+        if (e == cudaSuccess && positions_grad && !(flags & PERMUTO_KEEP_POSITIONS_GRAD))
             e = cudaMemsetAsync(positions_grad, 0, (size_t)a.p.n_points * cfg->pos_dim * sizeof(float), st);
         if (e != cudaSuccess) return cuda_fail(e, "permuto_backward clearing outputs");
     }

@@ -30,11 +30,14 @@ struct Simplex {
     float sorted_res[D + 1];  // residual/(D+1) of the coordinate whose rank is k
 };
 
-// pos: D floats.  shift, scale: this level's rows.  Rounding of every operation is explicit
-// so that the compiler cannot contract differently from the reference build:
-//   cf = (pos + shift) * scale            two roundings   (.cuh:134)
-//   elevated[i] = fma(-i, cf, sm)         one rounding    (.cuh:135 under nvcc's default -fmad)
-//   sm += cf                                              (.cuh:136)
+// pos: D floats.  shift, scale: this level's rows.  Rounding of every operation of the elevate
+// step is explicit, because simplex selection at fine levels hinges on single ulps of the
+// elevated coordinates (they reach 1e5..1e6).  The sequence below is what nvcc's default
+// -fmad=true makes of the reference source (.cuh:130-138), established by comparing against the
+// reference's own outputs for every pos_dim (cf_i = t_i*scale_i, t_i = pos_i + shift_i):
+//   i = D      : e[D] = -(D*cf_D), sm = cf_D
+//   2 <= i < D : e[i] = fma(-i, cf_i, sm), sm = sm + cf_i       (cf_i rounded, it feeds i*cf_i)
+//   i = 1      : e[1] = fma(-t_1, scale_1, sm), e[0] = fma(t_1, scale_1, sm)
 template <int D>
 __device__ __forceinline__ void locate_simplex(const float (&pos)[D], const float* __restrict__ shift,
                                                const float* __restrict__ scale, Simplex<D>& s) {
@@ -44,9 +47,21 @@ __device__ __forceinline__ void locate_simplex(const float (&pos)[D], const floa
     float sm = 0.0f;
 #pragma unroll
     for (int i = D; i > 0; --i) {
-        const float cf = __fmul_rn(__fadd_rn(pos[i - 1], __ldg(shift + i - 1)), __ldg(scale + i - 1));
-        e[i] = __fmaf_rn(-(float)i, cf, sm);
-        sm = __fadd_rn(sm, cf);
+        const float t = __fadd_rn(pos[i - 1], __ldg(shift + i - 1));
+        const float sc = __ldg(scale + i - 1);
+        if (i == 1) {
+            e[1] = __fmaf_rn(-t, sc, sm);
+            sm = __fmaf_rn(t, sc, sm);
+        } else {
+            const float cf = __fmul_rn(t, sc);
+            if (i == D) {
+                e[i] = -__fmul_rn((float)i, cf);
+                sm = cf;
+            } else {
+                e[i] = __fmaf_rn(-(float)i, cf, sm);
+                sm = __fadd_rn(sm, cf);
+            }
+        }
     }
     e[0] = sm;
 
@@ -134,13 +149,6 @@ __device__ __forceinline__ void vertex_hashes(const Simplex<D>& s, uint32_t (&h)
         }
         h[r] = base + (uint32_t)r * all - (uint32_t)(D + 1) * lowered;
     }
-}
-
-template <bool POW2>
-__device__ __forceinline__ uint32_t slot_of(uint32_t h, uint32_t capacity) {
-    // unsigned modulo (.cuh:34-36); capacity-1 is the mask when capacity is a power of two
-    if (POW2) return h & (capacity - 1u);
-    return h % capacity;
 }
 
 template <int D>

@@ -11,6 +11,8 @@ small and uniform, shifts ~ N(0, 10^2), scales a geometric progression.
 """
 from __future__ import annotations
 
+import zlib
+
 import numpy as np
 
 _MASK = np.uint64(0xFFFFFFFFFFFFFFFF)
@@ -98,17 +100,17 @@ def extra_levels(case: dict) -> int:
 def make_inputs(name: str) -> dict:
     """All input arrays of a case (float32 numpy)."""
     c = CASES[name]
-    k = sorted(CASES).index(name)
+    k = zlib.crc32(name.encode()) % 100000  # seed offset depends on the name only, not on the other cases
     d, cap, nl, n = c["pos_dim"], c["capacity"], c["nr_levels"], c["n"]
     width = 2 * (nl + extra_levels(c))
     lo, hi = c["box"]
     inputs = {
         "sigmas": sigmas_of(c),
-        "table": uniform((nl, cap, 2), 1000 + k, -c["table"], c["table"]),
-        "shift": normal((nl, d), 2000 + k, 10.0),
-        "positions": uniform((n, d), 3000 + k, lo, hi),
-        "grad_out": normal((n, width), 4000 + k, 1.0),
-        "dpg": normal((n, d), 5000 + k, 1.0),
+        "table": uniform((nl, cap, 2), 1000000 + k, -c["table"], c["table"]),
+        "shift": normal((nl, d), 2000000 + k, 10.0),
+        "positions": uniform((n, d), 3000000 + k, lo, hi),
+        "grad_out": normal((n, width), 4000000 + k, 1.0),
+        "dpg": normal((n, d), 5000000 + k, 1.0),
         "anneal": cosine_window(nl, c["window_t"]) if "window_t" in c else np.ones(nl, np.float32),
     }
     return inputs

@@ -1,0 +1,350 @@
+"""Parity of the CUDA path (called through the C ABI) with the oracle, with the fixtures made by
+the reference's own CUDA extension, and -- when the rebuilt reference extension is present --
+with the reference itself, live, on the same seeded inputs.
+
+Tolerances (stated by the task): lattice keys and hash slots bit-exact; features rtol 1e-5;
+gradients rtol 1e-4 (fp32 atomics accumulate in arbitrary order), applied to sum|addend|.
+"""
+import os
+import pickle
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from conftest import GOLDEN, densify
+
+pytestmark = pytest.mark.gpu
+
+FWD_RTOL, BWD_RTOL = 1e-5, 1e-4
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from permutohedral_encoding_b200 import _native
+    assert torch.cuda.is_available(), "these tests need the GPU; there is no CPU path"
+    return _native
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def table_bound(table_abs):
+    per_level = table_abs.reshape(table_abs.shape[0], -1).max(axis=1).reshape(-1, 1, 1)
+    return BWD_RTOL * table_abs + 1e-6 * per_level + 1e-30
+
+
+def make_encoding(nat, c, inp):
+    shift = T(inp["shift"])
+    fx = nat.EncodingFixedParams(c["pos_dim"], c["capacity"], c["nr_levels"], 2, inp["sigmas"], shift,
+                                 c.get("concat", False), c.get("points_scaling", 1.0))
+    return nat.EncodingWrapper.create(c["pos_dim"], 2, fx), fx
+
+
+def check_all(nat, oracle, c, inp, golden=None, parts=("forward", "backward", "double")):
+    d, cap = c["pos_dim"], c["capacity"]
+    concat = c.get("concat", False)
+    enc, fx = make_encoding(nat, c, inp)
+    scale = fx.m_scale_factor_host.numpy()
+    assert np.array_equal(scale.view(np.uint32), oracle.scale_factor(inp["sigmas"], d).view(np.uint32))
+    table, pos, anneal = T(inp["table"]), T(inp["positions"]), T(inp["anneal"])
+    I = nat.EncodingInput(table, pos, anneal, True, True)
+    oargs = (inp["positions"], inp["table"], scale, inp["shift"], inp["anneal"])
+
+    # geometry: bit-exact keys, slots, ranks; barycentric weights to fp32 rounding
+    dbg = enc.debug_lattice(I)
+    lat = oracle.lattice(inp["positions"], scale, inp["shift"], cap)
+    for k in ("keys", "slots", "rank"):
+        assert np.array_equal(dbg[k].cpu().numpy(), lat[k]), f"{k} differ from the oracle"
+    np.testing.assert_allclose(dbg["bary"].cpu().numpy(), lat["bary"], rtol=0, atol=1e-6)
+
+    out = enc.forward(I).cpu().numpy()
+    ref = oracle.forward(*oargs, concat_points=concat, points_scaling=c.get("points_scaling", 1.0))
+    np.testing.assert_allclose(out, ref, rtol=FWD_RTOL, atol=1e-6 * np.abs(ref).max())
+    if golden is not None:
+        g = golden["features"]
+        np.testing.assert_allclose(out, g, rtol=FWD_RTOL, atol=1e-6 * np.abs(g).max())
+
+    if "backward" in parts:
+        go = T(inp["grad_out"])
+        orc = oracle.backward(*oargs, inp["grad_out"], concat_points=concat, need_table=True, need_pos=True,
+                              need_abs=True)
+        bound = table_bound(orc["table_abs"])
+        for agg in (True, False):
+            enc.aggregate_collisions = agg
+            tg, pg = enc.backward(I, go)
+            assert np.all(np.abs(tg.cpu().numpy() - orc["table_grad"]) <= bound), f"table grad (aggregate={agg})"
+            np.testing.assert_allclose(pg.cpu().numpy(), orc["pos_grad"], rtol=BWD_RTOL,
+                                       atol=BWD_RTOL * np.abs(orc["pos_grad"]).max())
+        enc.aggregate_collisions = True
+        if golden is not None:
+            gt = densify(golden["table_grad_idx"], golden["table_grad_val"], inp["table"].shape)
+            assert np.all(np.abs(tg.cpu().numpy() - gt) <= bound)
+            np.testing.assert_allclose(pg.cpu().numpy(), golden["pos_grad"], rtol=BWD_RTOL,
+                                       atol=BWD_RTOL * np.abs(golden["pos_grad"]).max())
+        # only one of the two gradients requested
+        tg_only, none_pg = enc.backward(nat.EncodingInput(table, pos, anneal, True, False), go)
+        assert none_pg is None and np.all(np.abs(tg_only.cpu().numpy() - orc["table_grad"]) <= bound)
+        none_tg, pg_only = enc.backward(nat.EncodingInput(table, pos, anneal, False, True), go)
+        assert none_tg is None
+        np.testing.assert_allclose(pg_only.cpu().numpy(), orc["pos_grad"], rtol=BWD_RTOL,
+                                   atol=BWD_RTOL * np.abs(orc["pos_grad"]).max())
+
+    if "double" in parts:
+        go, dpg = T(inp["grad_out"]), T(inp["dpg"])
+        orc = oracle.double_backward(*oargs, inp["dpg"], inp["grad_out"], concat_points=concat, need_abs=True)
+        bound = table_bound(orc["table_abs"])
+        tg2, ggf = enc.double_backward_from_positions(I, dpg, go)
+        assert np.all(np.abs(tg2.cpu().numpy() - orc["table_grad"]) <= bound)
+        np.testing.assert_allclose(ggf.cpu().numpy(), orc["grad_grad_out"], rtol=BWD_RTOL,
+                                   atol=BWD_RTOL * np.abs(orc["grad_grad_out"]).max())
+        if golden is not None:
+            gt = densify(golden["dbl_table_grad_idx"], golden["dbl_table_grad_val"], inp["table"].shape)
+            assert np.all(np.abs(tg2.cpu().numpy() - gt) <= bound)
+            gg = golden["dbl_grad_grad_out"]
+            np.testing.assert_allclose(ggf.cpu().numpy(), gg, rtol=BWD_RTOL, atol=BWD_RTOL * np.abs(gg).max())
+        a, b = enc.double_backward_from_positions(I, dpg, go, need_lattice_grad=False)
+        assert a is None and torch.equal(b, ggf)
+        a, b = enc.double_backward_from_positions(I, dpg, go, need_grad_grad_features=False)
+        assert b is None and np.all(np.abs(a.cpu().numpy() - orc["table_grad"]) <= bound)
+
+
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_golden_cases(nat, oracle, name):
+    c = cases.CASES[name]
+    golden = np.load(os.path.join(GOLDEN, name + ".npz"))
+    check_all(nat, oracle, c, cases.make_inputs(name), golden, c["parts"])
+
+
+@pytest.mark.parametrize("d", [2, 3, 4, 5, 6, 7])
+def test_seeded_against_oracle(nat, oracle, d):
+    """Larger seeded inputs than the fixtures, every dimension, N not a multiple of the block."""
+    name = f"seeded_d{d}"
+    c = dict(pos_dim=d, capacity=2 ** 17, nr_levels=12, sigma=(1.0, 1e-3), n=20011, box=(-1.0, 1.0), table=1.0)
+    cases.CASES[name] = c
+    try:
+        inp = cases.make_inputs(name)
+    finally:
+        del cases.CASES[name]
+    check_all(nat, oracle, c, inp)
+
+
+def test_strided_positions(nat, oracle):
+    c = cases.CASES["window_d3"]
+    inp = cases.make_inputs("window_d3")
+    enc, fx = make_encoding(nat, c, inp)
+    table, anneal = T(inp["table"]), T(inp["anneal"])
+    wide = torch.zeros((c["n"], 8), device=DEV)
+    wide[:, 1:7:2] = T(inp["positions"])
+    view = wide[:, 1:7:2]  # strides (8, 2)
+    assert not view.is_contiguous()
+    a = enc.forward(nat.EncodingInput(table, view, anneal, False, False))
+    b = enc.forward(nat.EncodingInput(table, T(inp["positions"]), anneal, False, False))
+    assert torch.equal(a, b)
+    colmajor = T(inp["positions"]).t().contiguous().t()  # strides (1, n)
+    assert torch.equal(enc.forward(nat.EncodingInput(table, colmajor, anneal, False, False)), b)
+
+
+def _big(d, L, cap, n, lo, seed, box=(0.0, 1.0)):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    sig = np.geomspace(1.0, lo, L)
+    table = ((torch.rand((L, cap, 2), generator=gen) * 2 - 1) * 1e-4).to(DEV)
+    shift = (torch.randn((L, d), generator=gen) * 10).to(DEV)
+    pos = (torch.rand((n, d), generator=gen) * (box[1] - box[0]) + box[0]).to(DEV)
+    go = torch.randn((n, 2 * L), generator=gen).to(DEV)
+    dpg = torch.randn((n, d), generator=gen).to(DEV)
+    return sig, table, shift, pos, go, dpg
+
+
+def test_full_size_training_step_properties(nat):
+    """Training-step shape at full size (pos_dim 3, 24 levels, capacity 2^18, 2^20 points):
+    size-independent identities instead of an oracle run.  Forward is linear in the table, so
+    <grad_out, F(table)> = <table_grad, table>; results do not depend on collision merging or on
+    splitting the levels into buckets; forward is bitwise repeatable."""
+    d, L, cap, n = 3, 24, 2 ** 18, 2 ** 20
+    sig, table, shift, pos, go, _ = _big(d, L, cap, n, 1e-4, 11)
+    fx = nat.EncodingFixedParams(d, cap, L, 2, sig, shift, False, 1.0)
+    enc = nat.EncodingWrapper.create(d, 2, fx)
+    anneal = torch.ones(L, device=DEV)
+    I = nat.EncodingInput(table, pos, anneal, True, False)
+    out = enc.forward(I)
+    assert torch.equal(out, enc.forward(I))
+    tg, _ = enc.backward(I, go)
+    lhs = (go.double() * out.double()).sum().item()
+    rhs = (tg.double() * table.double()).sum().item()
+    scale = (go.double().abs() * out.double().abs()).sum().item()
+    assert abs(lhs - rhs) <= 1e-5 * scale
+    enc.aggregate_collisions = False
+    tg_plain, _ = enc.backward(I, go)
+    enc.aggregate_collisions = True
+    # per-entry sum|addend| is not available here; bound by rtol of the per-level magnitude
+    lvl = tg.abs().amax(dim=(1, 2), keepdim=True)
+    assert torch.all((tg - tg_plain).abs() <= BWD_RTOL * lvl + 1e-12)
+    tg_b = torch.empty_like(table)
+    for l0 in range(0, L, 8):
+        enc.backward(I, go, lattice_grad_out=tg_b, level_begin=l0, level_end=l0 + 8)
+    assert torch.all((tg - tg_b).abs() <= BWD_RTOL * lvl + 1e-12)
+    # every point contributes weight 1 per level: column sums of the gradient
+    ones = torch.ones_like(go)
+    tg1, _ = enc.backward(I, ones)
+    per_level = tg1.double().sum(dim=(1,))  # [L, 2]
+    assert torch.allclose(per_level, torch.full_like(per_level, float(n)), rtol=1e-4)
+
+
+def test_full_size_eikonal_properties(nat):
+    """Eikonal shape (capacity 2^19, 2^19 points in [-1,1)^3): the position gradient is bilinear
+    in (table, upstream gradient), so <dpg, pos_grad> = <dbl_table_grad, table> = <ggf, grad_out>."""
+    d, L, cap, n = 3, 24, 2 ** 19, 2 ** 19
+    sig, table, shift, pos, go, dpg = _big(d, L, cap, n, 1e-4, 12, box=(-1.0, 1.0))
+    fx = nat.EncodingFixedParams(d, cap, L, 2, sig, shift, False, 1.0)
+    enc = nat.EncodingWrapper.create(d, 2, fx)
+    anneal = torch.ones(L, device=DEV)
+    I = nat.EncodingInput(table, pos, anneal, True, True)
+    _, pg = enc.backward(I, go)
+    tg2, ggf = enc.double_backward_from_positions(I, dpg, go)
+    x = (dpg.double() * pg.double()).sum().item()
+    y = (tg2.double() * table.double()).sum().item()
+    z = (ggf.double() * go.double()).sum().item()
+    scale = (dpg.double().abs() * pg.double().abs()).sum().item()
+    assert abs(x - y) <= 1e-4 * scale and abs(x - z) <= 1e-4 * scale
+
+
+@pytest.mark.parametrize("d,L,cap,lo", [(3, 24, 2 ** 18, 1e-4), (4, 16, 2 ** 20, 1e-3), (6, 16, 2 ** 20, 1e-3)])
+def test_against_reference_extension_live(nat, d, L, cap, lo):
+    """Differential run against the reference's own CUDA extension rebuilt for sm_100 (present
+    when oracle/_ref was built where the reference sources are available)."""
+    from oracle import ref_shim
+    if not ref_shim.available():
+        pytest.skip("oracle/_ref/permuto_ref_C.so not present")
+    n = 2 ** 18
+    sig, table, shift, pos, go, dpg = _big(d, L, cap, n, lo, 20 + d)
+    table = table * 1e4  # O(1) values: any wrong slot shows as an O(1) error
+    anneal = torch.ones(L, device=DEV)
+    ref = ref_shim.RefEncoding(d, cap, L, sig, shift)
+    fx = nat.EncodingFixedParams(d, cap, L, 2, sig, shift, False, 1.0)
+    enc = nat.EncodingWrapper.create(d, 2, fx)
+    I = nat.EncodingInput(table, pos, anneal, True, True)
+
+    def rows(t):
+        return t.permute(2, 0, 1).reshape(t.shape[2], -1)
+
+    def lfn(r):
+        return r.reshape(r.shape[0], r.shape[1] // 2, 2).permute(1, 2, 0).contiguous()
+
+    f_ref = rows(ref.forward_raw(table, pos, anneal))
+    f_me = enc.forward(I)
+    assert torch.all((f_me - f_ref).abs() <= FWD_RTOL * f_ref.abs() + 1e-6 * f_ref.abs().max())
+    tg_ref, pg_ref = ref.backward_raw(table, pos, anneal, lfn(go), True, True)
+    tg, pg = enc.backward(I, go)
+    lvl = tg_ref.abs().amax(dim=(1, 2), keepdim=True)
+    assert torch.all((tg - tg_ref).abs() <= BWD_RTOL * lvl)
+    assert torch.all((pg - pg_ref).abs() <= BWD_RTOL * pg_ref.abs().max())
+    tg2_ref, ggs_ref = ref.double_backward_raw(table, pos, anneal, dpg, lfn(go))
+    tg2, ggf = enc.double_backward_from_positions(I, dpg, go)
+    lvl2 = tg2_ref.abs().amax(dim=(1, 2), keepdim=True)
+    assert torch.all((tg2 - tg2_ref).abs() <= BWD_RTOL * lvl2)
+    gg_ref = rows(ggs_ref)
+    assert torch.all((ggf - gg_ref).abs() <= BWD_RTOL * gg_ref.abs().max())
+
+
+# ---------------------------------------------------------------------------------------------
+# module level: the drop-in surface
+# ---------------------------------------------------------------------------------------------
+def build_module(c, inp):
+    from permutohedral_encoding_b200 import PermutoEncoding
+    m = PermutoEncoding(c["pos_dim"], c["capacity"], c["nr_levels"], 2, inp["sigmas"],
+                        concat_points=c.get("concat", False), concat_points_scaling=c.get("points_scaling", 1.0))
+    with torch.no_grad():
+        m.lattice_values.copy_(T(inp["table"]))
+        m.random_shift_per_level.copy_(T(inp["shift"]))
+    return m
+
+
+def test_module_surface_and_autograd(nat, oracle):
+    name = "window_d3"
+    c, inp = cases.CASES[name], cases.make_inputs(name)
+    m = build_module(c, inp)
+    assert m.lattice_values.shape == (c["nr_levels"], c["capacity"], 2)
+    assert m.random_shift_per_level.shape == (c["nr_levels"], 3)
+    assert sorted(m.state_dict()) == ["lattice_values", "random_shift_per_level"]
+    assert m.output_dims() == 2 * c["nr_levels"]
+    pos = T(inp["positions"]).requires_grad_(True)
+    window = T(inp["anneal"])
+    out = m(pos, window)
+    assert out.shape == (c["n"], m.output_dims())
+    scale = oracle.scale_factor(inp["sigmas"], 3)
+    oargs = (inp["positions"], inp["table"], scale, inp["shift"], inp["anneal"])
+    ref = oracle.forward(*oargs)
+    np.testing.assert_allclose(out.detach().cpu().numpy(), ref, rtol=FWD_RTOL, atol=1e-6 * np.abs(ref).max())
+    go = T(inp["grad_out"])
+    out.backward(go)
+    orc = oracle.backward(*oargs, inp["grad_out"], need_table=True, need_pos=True, need_abs=True)
+    assert m.lattice_values.grad.shape == m.lattice_values.shape and m.lattice_values.grad.is_contiguous()
+    assert np.all(np.abs(m.lattice_values.grad.cpu().numpy() - orc["table_grad"]) <= table_bound(orc["table_abs"]))
+    np.testing.assert_allclose(pos.grad.cpu().numpy(), orc["pos_grad"], rtol=BWD_RTOL,
+                               atol=BWD_RTOL * np.abs(orc["pos_grad"]).max())
+    assert m.random_shift_per_level.grad is None
+    # default window is all ones; no-grad forward works; wrong pos_dim raises like the reference
+    with torch.no_grad():
+        full = m(T(inp["positions"]))
+    ref1 = oracle.forward(inp["positions"], inp["table"], scale, inp["shift"], np.ones(c["nr_levels"], np.float32))
+    np.testing.assert_allclose(full.cpu().numpy(), ref1, rtol=FWD_RTOL, atol=1e-6 * np.abs(ref1).max())
+    with pytest.raises(RuntimeError, match="Pos dim"):
+        m(torch.zeros(4, 2, device=DEV))
+    with pytest.raises(RuntimeError, match="GPU memory"):
+        m(torch.zeros(4, 3))
+    with pytest.raises(RuntimeError, match="0 points"):
+        m(torch.zeros(0, 3, device=DEV))
+    # checkpoint and pickle round trips
+    m2 = build_module(c, dict(inp, table=inp["table"] * 0, shift=inp["shift"] * 0))
+    m2.load_state_dict(m.state_dict())
+    with torch.no_grad():
+        assert torch.equal(m2(T(inp["positions"])), full)
+    m3 = pickle.loads(pickle.dumps(m))
+    with torch.no_grad():
+        assert torch.equal(m3(T(inp["positions"])), full)
+
+
+def test_module_eikonal_double_backward(nat, oracle):
+    """PermutoSDF's eikonal term: y = F w, g = dy/dx with create_graph, loss = mean((|g|-1)^2),
+    then backward into the lattice values (reference: funcs.py:57-72)."""
+    name = "sdf_d3"
+    c, inp = cases.CASES[name], cases.make_inputs(name)
+    m = build_module(c, inp)
+    n, L = c["n"], c["nr_levels"]
+    w = cases.normal((2 * L,), 777, (1.0 / 48) ** 0.5)
+    pos = T(inp["positions"]).requires_grad_(True)
+    y = m(pos) @ T(w)
+    (g,) = torch.autograd.grad(y.sum(), pos, create_graph=True)
+    loss = ((g.norm(dim=1) - 1.0) ** 2).mean()
+    loss.backward()
+    scale = oracle.scale_factor(inp["sigmas"], 3)
+    anneal = np.ones(L, np.float32)
+    oargs = (inp["positions"], inp["table"], scale, inp["shift"], anneal)
+    go = np.tile(w.reshape(1, -1), (n, 1)).astype(np.float32)
+    pg = oracle.backward(*oargs, go, need_table=False, need_pos=True)["pos_grad"].astype(np.float64)
+    np.testing.assert_allclose(g.detach().cpu().numpy(), pg, rtol=BWD_RTOL, atol=BWD_RTOL * np.abs(pg).max())
+    norm = np.linalg.norm(pg, axis=1, keepdims=True)
+    dpg = (2.0 * (norm - 1.0) / n) * pg / norm
+    orc = oracle.double_backward(*oargs, dpg.astype(np.float32), go, need_abs=True)
+    got = m.lattice_values.grad.cpu().numpy()
+    assert np.all(np.abs(got - orc["table_grad"]) <= 5 * table_bound(orc["table_abs"]))
+    assert pos.grad is None or torch.count_nonzero(pos.grad) == 0  # piecewise linear: no Hessian term
+
+
+def test_module_first_order_only_through_positions(nat):
+    """Lattice frozen, gradient only to the positions; and lattice-only when positions do not
+    require grad."""
+    name = "train_d3"
+    c, inp = cases.CASES[name], cases.make_inputs(name)
+    m = build_module(c, inp)
+    m.lattice_values.requires_grad_(False)
+    pos = T(inp["positions"]).requires_grad_(True)
+    m(pos).sum().backward()
+    assert pos.grad is not None and m.lattice_values.grad is None
+    m.lattice_values.requires_grad_(True)
+    m(T(inp["positions"])).sum().backward()
+    assert m.lattice_values.grad is not None
