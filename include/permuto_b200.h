@@ -52,6 +52,9 @@ typedef struct permuto_config {
     int32_t capacity;          /* slots per level, any value >= 1 (power of two is faster)    */
     int32_t concat_points;     /* 0/1: append ceil(pos_dim/2) levels holding the raw points   */
     float points_scaling;      /* factor applied to the concatenated points                   */
+    int32_t levels_per_pass;   /* scheduling hint: levels one sweep over the points handles, a
+                                  multiple of 4; 0 = chosen from the capacity (no reference
+                                  counterpart; results do not depend on it)                    */
 } permuto_config;
 
 /* Per-call lattice inputs shared by every entry point.  Replaces the reference's

@@ -39,7 +39,8 @@ EXPORTED_SYMBOLS = (
 
 class PermutoConfig(C.Structure):
     _fields_ = [("pos_dim", C.c_int32), ("nr_feat_per_level", C.c_int32), ("nr_levels", C.c_int32),
-                ("capacity", C.c_int32), ("concat_points", C.c_int32), ("points_scaling", C.c_float)]
+                ("capacity", C.c_int32), ("concat_points", C.c_int32), ("points_scaling", C.c_float),
+                ("levels_per_pass", C.c_int32)]
 
 
 class PermutoInputs(C.Structure):
@@ -144,6 +145,8 @@ class EncodingFixedParams:
             raise RuntimeError("Encoding: pos_dim must be 2,3,4,5,6 or 7")
         self.m_scale_factor_host = torch.from_numpy(scale_factor(self.m_sigmas_list, self.m_pos_dim))
         self._scale_by_device = {}
+        # scheduling hint of the kernels (0 = automatic); PERMUTO_LEVELS_PER_PASS overrides it for experiments
+        self.levels_per_pass = int(os.environ.get("PERMUTO_LEVELS_PER_PASS", "0"))
 
     def scale_factor_on(self, device) -> torch.Tensor:
         device = torch.device(device)
@@ -155,7 +158,7 @@ class EncodingFixedParams:
 
     def config(self) -> PermutoConfig:
         return PermutoConfig(self.m_pos_dim, self.m_nr_feat_per_level, self.m_nr_levels, self.m_capacity,
-                             int(self.m_concat_points), self.m_points_scaling)
+                             int(self.m_concat_points), self.m_points_scaling, int(self.levels_per_pass))
 
 
 class EncodingWrapper:

@@ -67,6 +67,7 @@ int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::
     p.extra_levels = extra;
     p.points_scaling = cfg->points_scaling;
     p.rows_vec8_ok = 0;
+    p.levels_per_pass = cfg->levels_per_pass < 0 ? 0 : cfg->levels_per_pass;
     return PERMUTO_OK;
 }
 

@@ -33,8 +33,15 @@ __device__ __forceinline__ void load_pos(const Problem& p, int64_t n, float (&po
     for (int i = 0; i < D; ++i) pos[i] = __ldg(src + i * p.pos_stride_d);
 }
 
-__device__ __forceinline__ uint32_t to_slot(const Problem& p, uint32_t h) {
-    return p.cap_is_pow2 ? (h & (p.capacity - 1u)) : (h % p.capacity);
+// unsigned modulo by the capacity (EncodingGPU.cuh:34-36); a mask when it is a power of two
+__device__ __forceinline__ void to_slots(const Problem& p, const Simplex<D>& s, uint32_t (&slot)[D + 1]) {
+    if (p.cap_is_pow2) {
+#pragma unroll
+        for (int r = 0; r <= D; ++r) slot[r] = s.hash[r] & (p.capacity - 1u);
+    } else {
+#pragma unroll
+        for (int r = 0; r <= D; ++r) slot[r] = s.hash[r] % p.capacity;
+    }
 }
 
 // 8 consecutive floats of a feature row, 32-byte aligned
@@ -94,27 +101,30 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardArgs a) 
     const Problem& p = a.p;
     const int64_t n = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (n >= p.n_points) return;
-    const int l0 = p.level_begin + (int)blockIdx.y * LPT;
+    const int pass_begin = p.level_begin + (int)blockIdx.y * p.levels_per_pass;
+    const int pass_end = min(pass_begin + p.levels_per_pass, p.level_end);
 
     float pos[D];
     load_pos(p, n, pos);
 
+#pragma unroll 1
+    for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
     float out[2 * LPT];
 #pragma unroll
     for (int k = 0; k < LPT; ++k) {
         const int l = l0 + k;
         float ax = 0.f, ay = 0.f;
-        if (l < p.level_end) {  // uniform over the block
+        if (l < pass_end) {  // uniform over the block
             const float w_lvl = __ldg(p.anneal + l);
             if (w_lvl != 0.0f) {  // a closed coarse-to-fine window contributes exact zeros
                 Simplex<D> s;
                 locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-                uint32_t h[D + 1];
-                vertex_hashes<D>(s, h);
+                uint32_t slot[D + 1];
+                to_slots(p, s, slot);
                 const float* base = p.table + (size_t)l * p.capacity * 2u;
                 float2 v[D + 1];
 #pragma unroll
-                for (int r = 0; r <= D; ++r) v[r] = gather2(base, to_slot(p, h[r]));
+                for (int r = 0; r <= D; ++r) v[r] = gather2(base, slot[r]);
 #pragma unroll
                 for (int r = 0; r <= D; ++r) {
                     const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:234
@@ -127,6 +137,7 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardArgs a) 
         out[2 * k + 1] = ay;
     }
     store_row_segment<LPT>(p, a.features, n, l0, out);
+    }
 
     // raw points appended after the lattice levels (EncodingGPU.cuh:105-121)
     if (p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {
@@ -183,32 +194,35 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a
     const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     const bool active = n_raw < p.n_points;
     const int64_t n = active ? n_raw : p.n_points - 1;  // idle lanes shadow the last point
-    const int l0 = p.level_begin + (int)blockIdx.y * LPT;
+    const int pass_begin = p.level_begin + (int)blockIdx.y * p.levels_per_pass;
+    const int pass_end = min(pass_begin + p.levels_per_pass, p.level_end);
     const unsigned lane = threadIdx.x & 31u;
     constexpr float kInv = 1.0f / (D + 1);
 
     float pos[D];
     load_pos(p, n, pos);
-    float g[2 * LPT];
-    load_row_segment<LPT>(p, a.grad_features, n, l0, g);
 
     float dpos[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) dpos[i] = 0.f;
+    // Collisions inside a warp get rarer from one level to the next finer one: once a level of
+    // this group shows none, the remaining levels are not probed any more.
+    bool probe = a.aggregate != 0;
 
+#pragma unroll 1
+    for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
+    float g[2 * LPT];
+    load_row_segment<LPT>(p, a.grad_features, n, l0, g);
 #pragma unroll
     for (int k = 0; k < LPT; ++k) {
         const int l = l0 + k;
-        if (l >= p.level_end) continue;  // uniform
+        if (l >= pass_end) continue;  // uniform
         const float w_lvl = __ldg(p.anneal + l);
         if (w_lvl == 0.0f) continue;  // every addend of this level is an exact zero
         Simplex<D> s;
         locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-        uint32_t h[D + 1];
-        vertex_hashes<D>(s, h);
         uint32_t slot[D + 1];
-#pragma unroll
-        for (int r = 0; r <= D; ++r) slot[r] = to_slot(p, h[r]);
+        to_slots(p, s, slot);
         const float gx = g[2 * k], gy = g[2 * k + 1];
 
         if (POS) {
@@ -246,11 +260,12 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a
         if (TABLE) {
             float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
             bool merge = false;
-            if (a.aggregate) {
+            if (probe) {
                 // probe with vertex 0: if no two lanes share its slot the level is fine-grained
                 const uint32_t key = active ? slot[0] : (0xffffffffu - lane);
                 const unsigned grp = __match_any_sync(kFullMask, key);
                 merge = __reduce_max_sync(kFullMask, __popc(grp)) > 1;
+                probe = merge;
             }
 #pragma unroll
             for (int r = 0; r <= D; ++r) {
@@ -263,6 +278,7 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a
                 }
             }
         }
+    }
     }
     if (POS && active) {
         float* dst = a.positions_grad + n * D;
@@ -280,7 +296,8 @@ __global__ void __launch_bounds__(kThreads) double_backward_kernel(const DoubleB
     const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     const bool active = n_raw < p.n_points;
     const int64_t n = active ? n_raw : p.n_points - 1;
-    const int l0 = p.level_begin + (int)blockIdx.y * LPT;
+    const int pass_begin = p.level_begin + (int)blockIdx.y * p.levels_per_pass;
+    const int pass_end = min(pass_begin + p.levels_per_pass, p.level_end);
     const unsigned lane = threadIdx.x & 31u;
     constexpr float kInv = 1.0f / (D + 1);
 
@@ -288,24 +305,24 @@ __global__ void __launch_bounds__(kThreads) double_backward_kernel(const DoubleB
     load_pos(p, n, pos);
 #pragma unroll
     for (int i = 0; i < D; ++i) dpg[i] = __ldg(a.double_positions_grad + n * D + i);
+    bool probe = a.aggregate != 0;  // as in backward_kernel
+
+#pragma unroll 1
+    for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
     float g[2 * LPT];
     if (TABLE) load_row_segment<LPT>(p, a.grad_features, n, l0, g);
     float out[2 * LPT];
-
 #pragma unroll
     for (int k = 0; k < LPT; ++k) {
         const int l = l0 + k;
         float ox = 0.f, oy = 0.f;
-        if (l < p.level_end) {
+        if (l < pass_end) {
             const float w_lvl = __ldg(p.anneal + l);
             if (w_lvl != 0.0f) {
                 Simplex<D> s;
                 locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-                uint32_t h[D + 1];
-                vertex_hashes<D>(s, h);
                 uint32_t slot[D + 1];
-#pragma unroll
-                for (int r = 0; r <= D; ++r) slot[r] = to_slot(p, h[r]);
+                to_slots(p, s, slot);
 
                 // d loss / d elevated (EncodingGPU.cuh:1187-1199)
                 float gs[D], dE[D + 1];
@@ -348,10 +365,11 @@ __global__ void __launch_bounds__(kThreads) double_backward_kernel(const DoubleB
                     float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
                     const float gx = g[2 * k], gy = g[2 * k + 1];
                     bool merge = false;
-                    if (a.aggregate) {
+                    if (probe) {
                         const uint32_t key = active ? slot[0] : (0xffffffffu - lane);
                         const unsigned grp = __match_any_sync(kFullMask, key);
                         merge = __reduce_max_sync(kFullMask, __popc(grp)) > 1;
+                        probe = merge;
                     }
 #pragma unroll
                     for (int r = 0; r <= D; ++r) {
@@ -369,12 +387,11 @@ __global__ void __launch_bounds__(kThreads) double_backward_kernel(const DoubleB
         out[2 * k] = ox;
         out[2 * k + 1] = oy;
     }
-    if (GGF && active) {
-        store_row_segment<LPT>(p, a.grad_grad_features, n, l0, out);
-        if (p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {  // EncodingGPU.cuh:1290-1295
-            float* dst = a.grad_grad_features + n * p.width + 2 * p.nr_levels;
-            for (int c = 0; c < 2 * p.extra_levels; ++c) dst[c] = 0.f;
-        }
+    if (GGF && active) store_row_segment<LPT>(p, a.grad_grad_features, n, l0, out);
+    }
+    if (GGF && active && p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {  // EncodingGPU.cuh:1290-1295
+        float* dst = a.grad_grad_features + n * p.width + 2 * p.nr_levels;
+        for (int c = 0; c < 2 * p.extra_levels; ++c) dst[c] = 0.f;
     }
 }
 
@@ -390,8 +407,8 @@ __global__ void __launch_bounds__(kThreads) debug_kernel(const DebugArgs a) {
     load_pos(p, n, pos);
     Simplex<D> s;
     locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-    uint32_t h[D + 1];
-    vertex_hashes<D>(s, h);
+    uint32_t slot[D + 1];
+    to_slots(p, s, slot);
     const int64_t base = (n * p.nr_levels + l) * (D + 1);
 #pragma unroll
     for (int r = 0; r <= D; ++r) {
@@ -401,15 +418,44 @@ __global__ void __launch_bounds__(kThreads) debug_kernel(const DebugArgs a) {
 #pragma unroll
             for (int i = 0; i < D; ++i) a.keys[(base + r) * D + i] = key[i];
         }
-        if (a.slots) a.slots[base + r] = (int32_t)to_slot(p, h[r]);
+        if (a.slots) a.slots[base + r] = (int32_t)slot[r];
         if (a.bary) a.bary[base + r] = s.bary[r];
         if (a.rank) a.rank[base + r] = s.rank[r];
     }
 }
 
-inline dim3 grid_for(const Problem& p, int lpt) {
+// Levels handled by one thread in one sweep over the points.  A multiple of 4 (one 32-byte row
+// segment per inner step).  More levels per pass means fewer sweeps -- each sweep re-reads the
+// positions and touches only its own 32-byte pieces of every 128-byte line of the feature rows,
+// which costs a 4x DRAM over-fetch on the gradient reads with one group per sweep -- but a larger
+// set of table slices is live in L2 at once: capacity * 8 bytes per level for the values and as
+// much again for their gradient.  Measured on B200 (pos_dim 3 and 4, capacities 2^18..2^20):
+// scatter-only kernels are fastest with every level in one sweep even when the gradient table
+// exceeds L2; gather kernels want about 96 MB live, gather+scatter kernels about 64 MB.
+enum class Traffic { Gather, Scatter, Both };
+
+inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t) {
+    const int levels = p.level_end - p.level_begin;
+    int lpp = requested;
+    if (lpp <= 0) {
+        const double slice = 8.0 * p.capacity;
+        const double mb = 1024.0 * 1024.0;
+        if (t == Traffic::Scatter)
+            lpp = levels;
+        else if (t == Traffic::Gather)
+            lpp = (int)(96.0 * mb / slice);
+        else
+            lpp = (int)(64.0 * mb / (2.0 * slice));
+    }
+    lpp = (lpp / 4) * 4;
+    if (lpp < 4) lpp = 4;
+    if (lpp > levels) lpp = ((levels + 3) / 4) * 4;
+    return lpp;
+}
+
+inline dim3 grid_for(const Problem& p) {
     const unsigned gx = (unsigned)((p.n_points + kThreads - 1) / kThreads);
-    const unsigned gy = (unsigned)((p.level_end - p.level_begin + lpt - 1) / lpt);
+    const unsigned gy = (unsigned)((p.level_end - p.level_begin + p.levels_per_pass - 1) / p.levels_per_pass);
     return dim3(gx, gy, 1);
 }
 
@@ -420,22 +466,33 @@ inline bool use_single_level(const Problem& p) {
     return blocks4 < 2 * 148;
 }
 
+template <class Args>
+inline Args with_schedule(const Args& in, bool single, Traffic t) {
+    Args a = in;
+    a.p.levels_per_pass = single ? 1 : pick_levels_per_pass(a.p, a.p.levels_per_pass, t);
+    return a;
+}
+
 }  // namespace
 
 #define PERMUTO_CAT_(a, b) a##b
 #define PERMUTO_CAT(a, b) PERMUTO_CAT_(a, b)
 
-cudaError_t PERMUTO_CAT(launch_forward_dim, PERMUTO_DIM)(const ForwardArgs& a, cudaStream_t st) {
-    if (use_single_level(a.p))
-        forward_kernel<1><<<grid_for(a.p, 1), kThreads, 0, st>>>(a);
+cudaError_t PERMUTO_CAT(launch_forward_dim, PERMUTO_DIM)(const ForwardArgs& a0, cudaStream_t st) {
+    const bool single = use_single_level(a0.p);
+    const ForwardArgs a = with_schedule(a0, single, Traffic::Gather);
+    if (single)
+        forward_kernel<1><<<grid_for(a.p), kThreads, 0, st>>>(a);
     else
-        forward_kernel<4><<<grid_for(a.p, 4), kThreads, 0, st>>>(a);
+        forward_kernel<4><<<grid_for(a.p), kThreads, 0, st>>>(a);
     return cudaGetLastError();
 }
 
 template <int LPT>
-static cudaError_t launch_backward_lpt(const BackwardArgs& a, cudaStream_t st) {
-    const dim3 g = grid_for(a.p, LPT);
+static cudaError_t launch_backward_lpt(const BackwardArgs& a0, cudaStream_t st) {
+    const BackwardArgs a = with_schedule(
+        a0, LPT == 1, (a0.lattice_grad && a0.positions_grad) ? Traffic::Both : (a0.lattice_grad ? Traffic::Scatter : Traffic::Gather));
+    const dim3 g = grid_for(a.p);
     if (a.lattice_grad && a.positions_grad)
         backward_kernel<LPT, true, true><<<g, kThreads, 0, st>>>(a);
     else if (a.lattice_grad)
@@ -450,8 +507,11 @@ cudaError_t PERMUTO_CAT(launch_backward_dim, PERMUTO_DIM)(const BackwardArgs& a,
 }
 
 template <int LPT>
-static cudaError_t launch_double_lpt(const DoubleBackwardArgs& a, cudaStream_t st) {
-    const dim3 g = grid_for(a.p, LPT);
+static cudaError_t launch_double_lpt(const DoubleBackwardArgs& a0, cudaStream_t st) {
+    const DoubleBackwardArgs a = with_schedule(
+        a0, LPT == 1,
+        (a0.lattice_grad && a0.grad_grad_features) ? Traffic::Both : (a0.lattice_grad ? Traffic::Scatter : Traffic::Gather));
+    const dim3 g = grid_for(a.p);
     if (a.lattice_grad && a.grad_grad_features)
         double_backward_kernel<LPT, true, true><<<g, kThreads, 0, st>>>(a);
     else if (a.lattice_grad)

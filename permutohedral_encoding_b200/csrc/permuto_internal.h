@@ -25,6 +25,7 @@ struct Problem {
     int32_t extra_levels; // concat rows
     float points_scaling;
     int32_t rows_vec8_ok; // feature rows may be moved with 32-byte vector accesses
+    int32_t levels_per_pass; // in: requested (0 = automatic); set by the launcher for the kernel
 };
 
 struct ForwardArgs {
