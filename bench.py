@@ -68,9 +68,9 @@ WORKLOADS = {
     "sharded": dict(pos_dim=3, nr_levels=24, capacity=2 ** 19, total_points=2 ** 24, sigma=(1.0, 1e-4)),
 }
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant (backward) kernel on
-# the "train" workload, from the ncu capture summarised under profiles/; None = not captured.
-NCU_TRAFFIC_BYTES = {"train": None, "sharded": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch on the "train" workload, from the ncu
+# capture summarised in profiles/train_step_forward_backward_kernels.txt; None = not captured.
+NCU_TRAFFIC_BYTES = {"train": {"backward_kernel": 245.0e6, "forward_kernel": 202.5e6}, "sharded": None}
 
 
 class ClockSampler:
@@ -353,7 +353,7 @@ def main():
         dom = ("backward_kernel", ms_b, bytes_b) if ms_b >= ms_f else ("forward_kernel", ms_f, bytes_f)
         ach = dom[2] / (dom[1] * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "kernel": dom[0], "achieved": round(ach, 1), "peak": peak, "unit": "GB/s",
-                            "frac": round(ach / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(name),
+                            "frac": round(ach / peak, 4), "traffic": (NCU_TRAFFIC_BYTES.get(name) or {}).get(dom[0]),
                             "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                             "algorithmic_bytes_per_launch": dom[2], "ms_per_launch": round(dom[1], 4),
                             "forward_kernel": {"ms": round(ms_f, 4), "achieved": round(bytes_f / (ms_f * 1e-3) / 1e9, 1)},

@@ -1,0 +1,74 @@
+"""Two-GPU check of the data-parallel path: points sharded, lattice replicated, lattice gradient
+all-reduced bucket by bucket while backward is still running.  Skipped with fewer than 2 GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from permutohedral_encoding_b200 import PermutoEncoding
+    from permutohedral_encoding_b200.distributed import LatticeGradAllReduce, shard_bounds
+    d, cap, nl, n = 3, 2 ** 16, 12, 50001
+    gen = torch.Generator().manual_seed(5)
+    table = (torch.rand((nl, cap, 2), generator=gen) * 2 - 1).to(dev)
+    shift = (torch.randn((nl, d), generator=gen) * 10).to(dev)
+    pos_all = torch.rand((n, d), generator=gen).to(dev)
+    go_all = torch.randn((n, 2 * nl), generator=gen).to(dev)
+    torch.manual_seed(0)
+    m = PermutoEncoding(d, cap, nl, 2, np.geomspace(1.0, 1e-3, nl))
+    with torch.no_grad():
+        m.lattice_values.copy_(table)
+        m.random_shift_per_level.copy_(shift)
+    # the whole batch on this GPU alone
+    pos = pos_all.clone().requires_grad_(True)
+    out_full = m(pos)
+    out_full.backward(go_all)
+    full_tg, full_pg = m.lattice_values.grad.clone(), pos.grad.clone()
+    m.lattice_values.grad = None
+    # this rank's shard with the bucketed all-reduce
+    hook = LatticeGradAllReduce(m, nr_buckets=3)
+    b, e = shard_bounds(n, rank, world)
+    pos_s = pos_all[b:e].clone().requires_grad_(True)
+    out_s = m(pos_s)
+    out_s.backward(go_all[b:e])
+    torch.cuda.synchronize()
+    lvl = full_tg.abs().amax(dim=(1, 2), keepdim=True)
+    ok_tg = bool(torch.all((m.lattice_values.grad - full_tg).abs() <= 1e-4 * lvl))
+    ok_out = bool(torch.equal(out_s, out_full[b:e]))
+    ok_pg = bool(torch.all((pos_s.grad - full_pg[b:e]).abs() <= 1e-4 * full_pg.abs().max()))
+    hook.remove()
+    torch.save({"ok": (ok_tg, ok_out, ok_pg)}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_step_matches_single_gpu(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert torch.load(tmp_path / f"r{r}.pt")["ok"] == (True, True, True)
