@@ -43,6 +43,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "train", "sharded"])
     ap.add_argument("--buckets", type=int, default=3, help="level buckets of the overlapped all-reduce")
+    ap.add_argument("--bucket-policy", default="halving", choices=["halving", "even"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -146,7 +147,7 @@ class OursStep:
         with torch.no_grad():
             self.m.lattice_values.copy_(table)
             self.m.random_shift_per_level.copy_(shift)
-        self.hook = LatticeGradAllReduce(self.m, nr_buckets=buckets) if world > 1 else None
+        self.hook = LatticeGradAllReduce(self.m, nr_buckets=buckets, policy=ARGS.bucket_policy) if world > 1 else None
         self.launches_per_step = 2 if world == 1 else 1 + len(self.hook.buckets)
 
     def step(self, pos, grad_out):
@@ -283,7 +284,8 @@ def main():
     torch.cuda.set_device(LOCAL_DEVICE)
     device = torch.device("cuda", LOCAL_DEVICE)
     if WORLD > 1:
-        dist.init_process_group("nccl", device_id=device)
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)  # collectives beside the backward kernels
+        dist.init_process_group("nccl", device_id=device, pg_options=opts)
     assert WORLD == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={WORLD}: launch with torchrun for N > 1"
 
     total = w["total_points"]

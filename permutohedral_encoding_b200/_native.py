@@ -21,7 +21,8 @@ import numpy as np
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libpermuto_b200.so")
+# PERMUTO_B200_LIB points at another build of the same library (e.g. one made with other tuning macros)
+LIB_PATH = os.environ.get("PERMUTO_B200_LIB") or os.path.join(_PKG_DIR, "libpermuto_b200.so")
 
 PERMUTO_OK = 0
 PERMUTO_ERR_INVALID_ARGUMENT = -1

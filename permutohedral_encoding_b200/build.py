@@ -50,12 +50,19 @@ def _run(cmd, verbose):
     return res.stdout
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
-    """Build if sources are newer than the library; returns the library path."""
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, defines=(), out: str | None = None) -> str:
+    """Build if sources are newer than the library; returns the library path.  ``defines`` adds
+    -D macros (tuning experiments) and ``out`` writes the library elsewhere."""
+    global OBJ_DIR, LIB_PATH
+    if out:
+        LIB_PATH = os.path.abspath(out)
+        OBJ_DIR = LIB_PATH + ".obj"
+        force = True
     if not force and not _stale():
         return LIB_PATH
     os.makedirs(OBJ_DIR, exist_ok=True)
     flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + ["-I", INCLUDE, "-I", CSRC]
+    flags += [f"-D{d}" for d in defines]
     if ptxas_info:
         flags += ["-Xptxas", "-v"]
     jobs = []
@@ -83,8 +90,10 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills per kernel")
+    ap.add_argument("-D", dest="defines", action="append", default=[], help="extra macro, e.g. -D PERMUTO_THREADS=128")
+    ap.add_argument("--out", default=None, help="write the library to this path instead")
     args = ap.parse_args()
-    print(build(force=args.force, verbose=True, ptxas_info=args.ptxas_info))
+    print(build(force=args.force, verbose=True, ptxas_info=args.ptxas_info, defines=args.defines, out=args.out))
     return 0
 
 

@@ -24,7 +24,13 @@ namespace permuto {
 namespace {
 
 constexpr int D = PERMUTO_DIM;
-constexpr int kThreads = 256;
+#ifndef PERMUTO_THREADS
+#define PERMUTO_THREADS 256
+#endif
+#ifndef PERMUTO_MIN_BLOCKS
+#define PERMUTO_MIN_BLOCKS 1
+#endif
+constexpr int kThreads = PERMUTO_THREADS;
 constexpr unsigned kFullMask = 0xffffffffu;
 
 __device__ __forceinline__ void load_pos(const Problem& p, int64_t n, float (&pos)[D]) {
@@ -97,7 +103,7 @@ __device__ __forceinline__ void store_row_segment(const Problem& p, float* rows,
 // forward
 // ------------------------------------------------------------------------------------------
 template <int LPT>
-__global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardArgs a) {
+__global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) forward_kernel(const ForwardArgs a) {
     const Problem& p = a.p;
     const int64_t n = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (n >= p.n_points) return;
@@ -152,36 +158,66 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardArgs a) 
 }
 
 // ------------------------------------------------------------------------------------------
-// scatter-add of one table-gradient entry per lane, colliding lanes merged first
+// scatter-add of the d+1 table-gradient entries of one level, colliding lanes merged first
 // ------------------------------------------------------------------------------------------
 // On coarse levels the 32 points of a warp hit a handful of slots; sending 32 same-address
-// reductions to L2 serialises there.  match.any groups the lanes by slot, a pointer-jumping
-// suffix sum over each group's lanes (log2 of the largest group rounds) leaves the group total
-// in its lowest lane, and only that lane issues the vector reduction.  The summation order is
-// fixed by the lane order, so a warp's contribution is deterministic.
-__device__ __forceinline__ void scatter_merged(float* level_base, uint32_t slot, float x, float y, bool active,
-                                               unsigned lane) {
-    const uint32_t key = active ? slot : (0xffffffffu - lane);  // idle lanes match nobody
-    const unsigned group = __match_any_sync(kFullMask, key);
+// reductions to L2 serialises there (2.0-3.6 ms per backward instead of 0.47 on the training
+// shape).  match.any groups the lanes by slot, a pointer-jumping suffix sum over each group's
+// lanes (log2 of the largest group rounds) leaves the group total in its lowest lane, and only
+// that lane issues the vector reduction.  The summation order is fixed by the lane order, so a
+// warp's contribution is deterministic.
+__device__ __forceinline__ void merge_and_red(float* level_base, uint32_t slot, float x, float y, bool active,
+                                              unsigned lane, unsigned group) {
     const int largest = __reduce_max_sync(kFullMask, __popc(group));
-    if (largest > 1) {  // warp-uniform
-        const unsigned above = group & (0xfffffffeu << lane);
-        int next = above ? (__ffs(above) - 1) : -1;
-        for (int span = 1; span < largest; span <<= 1) {
-            const int src = next >= 0 ? next : (int)lane;
-            const float x2 = __shfl_sync(kFullMask, x, src);
-            const float y2 = __shfl_sync(kFullMask, y, src);
-            const int n2 = __shfl_sync(kFullMask, next, src);
-            if (next >= 0) {
-                x += x2;
-                y += y2;
-                next = n2;
-            }
+    const unsigned above = group & (0xfffffffeu << lane);
+    int next = above ? (__ffs(above) - 1) : -1;
+    for (int span = 1; span < largest; span <<= 1) {  // warp-uniform trip count
+        const int src = next >= 0 ? next : (int)lane;
+        const float x2 = __shfl_sync(kFullMask, x, src);
+        const float y2 = __shfl_sync(kFullMask, y, src);
+        const int n2 = __shfl_sync(kFullMask, next, src);
+        if (next >= 0) {
+            x += x2;
+            y += y2;
+            next = n2;
         }
-        const bool leader = (group & ((1u << lane) - 1u)) == 0u;
-        if (leader && active) red_add2(level_base, slot, x, y);
-    } else if (active) {
-        red_add2(level_base, slot, x, y);
+    }
+    const bool leader = (group & ((1u << lane) - 1u)) == 0u;
+    if (leader && active) red_add2(level_base, slot, x, y);
+}
+
+// Merging pays only while a warp's 32 points share slots: per warp and vertex the number of
+// distinct slots on the training shape is 6, 7, 9, 15, 22, 38, 63, 96, 116, 124 of 128 for levels
+// 0..9 and 128 from level 11 on, and match.any itself is slowest when all keys differ.  The
+// match of vertex 0 doubles as the probe: when it finds more than kMergeBelow distinct slots the
+// level is scattered directly and -- collisions only get rarer towards finer levels -- the warp
+// stops probing for the rest of its pass (`probe` is warp-uniform state owned by the caller).
+#ifndef PERMUTO_MERGE_BELOW
+#define PERMUTO_MERGE_BELOW 24
+#endif
+constexpr int kMergeBelow = PERMUTO_MERGE_BELOW;
+
+__device__ __forceinline__ void scatter_level(float* level_base, const uint32_t (&slot)[D + 1], const float (&ax)[D + 1],
+                                              const float (&ay)[D + 1], bool active, unsigned lane, bool& probe) {
+    if (probe) {
+        const uint32_t idle = 0xffffffffu - lane;  // idle lanes match nobody
+        const unsigned group0 = __match_any_sync(kFullMask, active ? slot[0] : idle);
+        const bool leader0 = (group0 & ((1u << lane) - 1u)) == 0u;
+        const int distinct = __popc(__ballot_sync(kFullMask, leader0));
+        if (distinct <= kMergeBelow) {
+            merge_and_red(level_base, slot[0], ax[0], ay[0], active, lane, group0);
+#pragma unroll
+            for (int r = 1; r <= D; ++r) {
+                const unsigned group = __match_any_sync(kFullMask, active ? slot[r] : idle);
+                merge_and_red(level_base, slot[r], ax[r], ay[r], active, lane, group);
+            }
+            return;
+        }
+        probe = false;
+    }
+    if (active) {
+#pragma unroll
+        for (int r = 0; r <= D; ++r) red_add2(level_base, slot[r], ax[r], ay[r]);
     }
 }
 
@@ -189,7 +225,7 @@ __device__ __forceinline__ void scatter_merged(float* level_base, uint32_t slot,
 // first-order backward: table gradient (scatter) and/or position gradient (gather)
 // ------------------------------------------------------------------------------------------
 template <int LPT, bool TABLE, bool POS>
-__global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a) {
+__global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) backward_kernel(const BackwardArgs a) {
     const Problem& p = a.p;
     const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     const bool active = n_raw < p.n_points;
@@ -205,8 +241,6 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a
     float dpos[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) dpos[i] = 0.f;
-    // Collisions inside a warp get rarer from one level to the next finer one: once a level of
-    // this group shows none, the remaining levels are not probed any more.
     bool probe = a.aggregate != 0;
 
 #pragma unroll 1
@@ -259,24 +293,14 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a
 
         if (TABLE) {
             float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
-            bool merge = false;
-            if (probe) {
-                // probe with vertex 0: if no two lanes share its slot the level is fine-grained
-                const uint32_t key = active ? slot[0] : (0xffffffffu - lane);
-                const unsigned grp = __match_any_sync(kFullMask, key);
-                merge = __reduce_max_sync(kFullMask, __popc(grp)) > 1;
-                probe = merge;
-            }
+            float ax[D + 1], ay[D + 1];
 #pragma unroll
             for (int r = 0; r <= D; ++r) {
                 const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:405-410
-                const float ax = gx * w, ay = gy * w;
-                if (merge) {
-                    scatter_merged(gbase, slot[r], ax, ay, active, lane);
-                } else if (active) {
-                    red_add2(gbase, slot[r], ax, ay);
-                }
+                ax[r] = gx * w;
+                ay[r] = gy * w;
             }
+            scatter_level(gbase, slot, ax, ay, active, lane, probe);
         }
     }
     }
@@ -291,7 +315,7 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(const BackwardArgs a
 // double backward of the position gradient
 // ------------------------------------------------------------------------------------------
 template <int LPT, bool TABLE, bool GGF>
-__global__ void __launch_bounds__(kThreads) double_backward_kernel(const DoubleBackwardArgs a) {
+__global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) double_backward_kernel(const DoubleBackwardArgs a) {
     const Problem& p = a.p;
     const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     const bool active = n_raw < p.n_points;
@@ -364,23 +388,14 @@ __global__ void __launch_bounds__(kThreads) double_backward_kernel(const DoubleB
                 if (TABLE) {
                     float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
                     const float gx = g[2 * k], gy = g[2 * k + 1];
-                    bool merge = false;
-                    if (probe) {
-                        const uint32_t key = active ? slot[0] : (0xffffffffu - lane);
-                        const unsigned grp = __match_any_sync(kFullMask, key);
-                        merge = __reduce_max_sync(kFullMask, __popc(grp)) > 1;
-                        probe = merge;
-                    }
+                    float ax[D + 1], ay[D + 1];
 #pragma unroll
                     for (int r = 0; r <= D; ++r) {
                         const float c = dB[r] * w_lvl;  // EncodingGPU.cuh:1244-1245
-                        const float ax = c * gx, ay = c * gy;
-                        if (merge) {
-                            scatter_merged(gbase, slot[r], ax, ay, active, lane);
-                        } else if (active) {
-                            red_add2(gbase, slot[r], ax, ay);
-                        }
+                        ax[r] = c * gx;
+                        ay[r] = c * gy;
                     }
+                    scatter_level(gbase, slot, ax, ay, active, lane, probe);
                 }
             }
         }

@@ -29,16 +29,33 @@ def shard_bounds(nr_positions: int, rank: int, world_size: int) -> Tuple[int, in
     return begin, begin + base + (1 if rank < rem else 0)
 
 
-def level_buckets(nr_levels: int, nr_buckets: int) -> List[Tuple[int, int]]:
+def level_buckets(nr_levels: int, nr_buckets: int, policy: str = "halving") -> List[Tuple[int, int]]:
     """Split levels into at most ``nr_buckets`` contiguous buckets whose boundaries are multiples
-    of 4 levels (the kernels' level-group size), coarse levels first."""
+    of 4 levels (the kernels' level-group size), coarse levels first.
+
+    ``policy="halving"`` (default) makes every bucket about half as long as the one before: the
+    all-reduce of a bucket overlaps the backward of the remaining, shorter buckets, and only the
+    last, smallest bucket's all-reduce is exposed, while most levels still run in one long sweep
+    (long sweeps are the efficient ones).  ``policy="even"`` gives equal buckets."""
     groups = (nr_levels + 3) // 4
     nr_buckets = max(1, min(int(nr_buckets), groups))
+    if policy == "even":
+        sizes = [groups // nr_buckets + (1 if b < groups % nr_buckets else 0) for b in range(nr_buckets)]
+    elif policy == "halving":
+        weights = [2.0 ** (nr_buckets - 1 - b) for b in range(nr_buckets)]
+        total = sum(weights)
+        sizes = [1] * nr_buckets                       # every bucket gets at least one group
+        spare = groups - nr_buckets
+        ideal = [w / total * groups for w in weights]
+        for _ in range(spare):                         # hand out the rest by largest deficit
+            b = max(range(nr_buckets), key=lambda i: (ideal[i] - sizes[i], -i))
+            sizes[b] += 1
+    else:
+        raise ValueError(f"unknown bucket policy {policy!r}")
     out, g0 = [], 0
-    for b in range(nr_buckets):
-        g1 = g0 + groups // nr_buckets + (1 if b < groups % nr_buckets else 0)
-        out.append((g0 * 4, min(g1 * 4, nr_levels)))
-        g0 = g1
+    for sz in sizes:
+        out.append((g0 * 4, min((g0 + sz) * 4, nr_levels)))
+        g0 += sz
     return [(a, b) for a, b in out if b > a]
 
 
@@ -49,11 +66,12 @@ class LatticeGradAllReduce:
     After ``loss.backward()`` the parameter's ``.grad`` holds the sum over ranks (or the mean
     with ``average=True``).  Call ``remove()`` to restore single-GPU behaviour."""
 
-    def __init__(self, encoding, process_group=None, nr_buckets: int = 3, average: bool = False):
+    def __init__(self, encoding, process_group=None, nr_buckets: int = 3, average: bool = False,
+                 policy: str = "halving"):
         self.encoding = encoding
         self.group = process_group
         self.average = average
-        self.buckets = level_buckets(encoding.nr_levels, nr_buckets)
+        self.buckets = level_buckets(encoding.nr_levels, nr_buckets, policy)
         encoding.lattice.backward_hook = self._backward
         self.last_works = []
 

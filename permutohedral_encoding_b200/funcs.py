@@ -29,6 +29,12 @@ class PermutoEncodingFunc(torch.autograd.Function):
     def backward(ctx, grad_sliced_values):
         lattice_values, positions, anneal_window = ctx.saved_tensors
         req_lv, req_pos = ctx.require
+        # only what this backward pass was asked for: autograd.grad(y, positions) does not need the
+        # lattice gradient (the reference computes and discards it)
+        req_lv = req_lv and ctx.needs_input_grad[1]
+        req_pos = req_pos and ctx.needs_input_grad[2]
+        if not (req_lv or req_pos) and any(ctx.require):
+            return None, None, None, None, None, None
         assert req_lv or req_pos, (
             "We cannot perform the backward function on the slicing because we did not precompute the required "
             "tensors in the forward pass. To enable this, set the model.train(), set torch.set_grad_enabled(True) "

@@ -51,12 +51,18 @@ def test_shard_bounds_cover_exactly():
 
 def test_level_buckets():
     from permutohedral_encoding_b200.distributed import level_buckets
-    assert level_buckets(24, 3) == [(0, 8), (8, 16), (16, 24)]
+    assert level_buckets(24, 3, "even") == [(0, 8), (8, 16), (16, 24)]
+    assert level_buckets(24, 3) == [(0, 12), (12, 20), (20, 24)]
+    assert level_buckets(24, 2) == [(0, 16), (16, 24)]
+    assert level_buckets(24, 1) == [(0, 24)]
     assert level_buckets(10, 8) == [(0, 4), (4, 8), (8, 10)]
     assert level_buckets(3, 2) == [(0, 3)]
+    with pytest.raises(ValueError):
+        level_buckets(8, 2, "nope")
     for nl in range(1, 40):
         for nb in range(1, 9):
-            bk = level_buckets(nl, nb)
+          for pol in ("halving", "even"):
+            bk = level_buckets(nl, nb, pol)
             assert bk[0][0] == 0 and bk[-1][1] == nl
             assert all(a[1] == b[0] for a, b in zip(bk, bk[1:]))
             assert all(a % 4 == 0 for a, _ in bk)
