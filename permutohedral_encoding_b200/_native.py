@@ -105,11 +105,37 @@ def extra_levels(pos_dim: int, concat_points: bool) -> int:
 
 
 def _ptr(t):
-    return None if t is None else C.c_void_p(t.data_ptr())
+    # plain integers are accepted for the void* parameters (argtypes are declared)
+    return None if t is None else t.data_ptr()
 
 
-def _stream(device) -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream(device):
+    """Handle of the current CUDA stream of ``device`` as an integer."""
+    if _raw_stream is not None:
+        return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _guard(device):
+    """Device guard that costs nothing when ``device`` is already current (the usual case; the
+    small README-sized calls are dominated by host overhead)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
 
 
 class EncodingInput:
@@ -158,8 +184,12 @@ class EncodingFixedParams:
         return t
 
     def config(self) -> PermutoConfig:
-        return PermutoConfig(self.m_pos_dim, self.m_nr_feat_per_level, self.m_nr_levels, self.m_capacity,
-                             int(self.m_concat_points), self.m_points_scaling, int(self.levels_per_pass))
+        cached = self.__dict__.get("_cfg")
+        if cached is None or cached.levels_per_pass != int(self.levels_per_pass):
+            cached = PermutoConfig(self.m_pos_dim, self.m_nr_feat_per_level, self.m_nr_levels, self.m_capacity,
+                                   int(self.m_concat_points), self.m_points_scaling, int(self.levels_per_pass))
+            self._cfg = cached
+        return cached
 
 
 class EncodingWrapper:
@@ -173,6 +203,7 @@ class EncodingWrapper:
                 "Encoding: nr_feat_per_level must be 2 since other values are not yet implemented")
         self.fixed = fixed_params
         self.aggregate_collisions = True
+        self._width = 2 * (fixed_params.m_nr_levels + extra_levels(fixed_params.m_pos_dim, fixed_params.m_concat_points))
 
     @staticmethod
     def create(pos_dim, nr_feat_per_level, fixed_params) -> "EncodingWrapper":
@@ -222,8 +253,7 @@ class EncodingWrapper:
         return ins, keep
 
     def output_width(self) -> int:
-        fp = self.fixed
-        return 2 * (fp.m_nr_levels + extra_levels(fp.m_pos_dim, fp.m_concat_points))
+        return self._width
 
     def _flags(self, zero=True) -> int:
         f = PERMUTO_ZERO_OUTPUTS if zero else 0
@@ -238,7 +268,7 @@ class EncodingWrapper:
         pos = inp.m_positions_raw
         cfg = self.fixed.config()
         out = torch.empty((pos.shape[0], self.output_width()), dtype=torch.float32, device=pos.device)
-        with torch.cuda.device(pos.device):
+        with _guard(pos.device):
             ins, keep = self._inputs(inp)
             check(lib.permuto_forward(C.byref(cfg), C.byref(ins), _ptr(out), _stream(pos.device)))
         return out
@@ -272,7 +302,7 @@ class EncodingWrapper:
                 pos_grad = torch.empty((n, fp.m_pos_dim), dtype=torch.float32, device=pos.device)
         lb = 0 if level_begin is None else int(level_begin)
         le = fp.m_nr_levels if level_end is None else int(level_end)
-        with torch.cuda.device(pos.device):
+        with _guard(pos.device):
             ins, keep = self._inputs(inp)
             check(lib.permuto_backward(C.byref(cfg), C.byref(ins), _ptr(grad_features), _ptr(lv_grad), _ptr(pos_grad),
                                        lb, le, flags, _stream(pos.device)))
@@ -296,7 +326,7 @@ class EncodingWrapper:
         cfg = fp.config()
         lv_grad = torch.empty_like(inp.m_lattice_values) if need_lattice_grad else None
         ggf = torch.empty_like(gf) if need_grad_grad_features else None
-        with torch.cuda.device(pos.device):
+        with _guard(pos.device):
             ins, keep = self._inputs(inp)
             check(lib.permuto_double_backward(C.byref(cfg), C.byref(ins), _ptr(dpg), _ptr(gf), _ptr(lv_grad),
                                               _ptr(ggf), self._flags(True), _stream(pos.device)))
@@ -314,7 +344,7 @@ class EncodingWrapper:
         bary = torch.empty((n, nl, d + 1), dtype=torch.float32, device=dev) if "bary" in want else None
         rank = torch.empty((n, nl, d + 1), dtype=torch.int32, device=dev) if "rank" in want else None
         cfg = fp.config()
-        with torch.cuda.device(dev):
+        with _guard(dev):
             ins, keep = self._inputs(inp)
             check(lib.permuto_debug_lattice(C.byref(cfg), C.byref(ins), _ptr(keys), _ptr(slots), _ptr(bary),
                                             _ptr(rank), _stream(dev)))

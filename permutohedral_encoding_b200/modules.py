@@ -74,12 +74,18 @@ class PermutoEncoding(torch.nn.Module):
     def forward(self, positions, anneal_window=None):
         if anneal_window is None:
             anneal_window = self.anneal_window
-        anneal_window = anneal_window.to(positions.device)
+        if anneal_window.device != positions.device:
+            anneal_window = anneal_window.to(positions.device)
         # the shift parameter may have been replaced (load_state_dict(assign=True), .to())
         self.fixed_params.m_random_shift_per_level = self.random_shift_per_level
 
-        require_lattice_values_grad = self.lattice_values.requires_grad and torch.is_grad_enabled()
-        require_positions_grad = positions.requires_grad and torch.is_grad_enabled()
+        grad_mode = torch.is_grad_enabled()
+        require_lattice_values_grad = self.lattice_values.requires_grad and grad_mode
+        require_positions_grad = positions.requires_grad and grad_mode
+        if not (require_lattice_values_grad or require_positions_grad):
+            # inference: nothing to record, skip the autograd machinery (host overhead dominates
+            # README-sized batches)
+            return self.lattice.forward(_C.EncodingInput(self.lattice_values, positions, anneal_window, False, False))
 
         # [N, (L+extra)*F] already in the reference's output order: no permute/reshape copy
         return PermutoEncodingFunc.apply(self.lattice, self.lattice_values, positions, anneal_window,

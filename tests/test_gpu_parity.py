@@ -348,3 +348,25 @@ def test_module_first_order_only_through_positions(nat):
     m.lattice_values.requires_grad_(True)
     m(T(inp["positions"])).sum().backward()
     assert m.lattice_values.grad is not None
+
+
+def test_host_point_feeder_keeps_batches_apart(nat):
+    """The double-buffered host feed hands out batches in submission order and never lets a copy
+    overwrite a buffer that enqueued work still reads."""
+    from permutohedral_encoding_b200.host_feed import HostPointFeeder
+    feeder = HostPointFeeder(DEV)
+    batches = [torch.full((4096, 3), float(i)).pin_memory() for i in range(6)]
+    feeder.submit(batches[0])
+    sums = []
+    for i in range(6):
+        x = feeder.next()
+        if i + 1 < 6:
+            feeder.submit(batches[i + 1])
+        y = x.clone()
+        for _ in range(20):          # keep the consumer busy while the next copy is in flight
+            y = y * 1.0
+        sums.append(y.sum())
+    torch.cuda.synchronize()
+    assert [float(s) for s in sums] == [float(i) * 4096 * 3 for i in range(6)]
+    with pytest.raises(RuntimeError):
+        feeder.next()
