@@ -42,7 +42,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "train", "sharded"])
-    ap.add_argument("--buckets", type=int, default=3, help="level buckets of the overlapped all-reduce")
+    ap.add_argument("--buckets", type=int, default=2, help="level buckets of the overlapped all-reduce")
+    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "multimem"])
     ap.add_argument("--bucket-policy", default="halving", choices=["halving", "even"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -147,7 +148,10 @@ class OursStep:
         with torch.no_grad():
             self.m.lattice_values.copy_(table)
             self.m.random_shift_per_level.copy_(shift)
-        self.hook = LatticeGradAllReduce(self.m, nr_buckets=buckets, policy=ARGS.bucket_policy) if world > 1 else None
+        mm = {"auto": "auto", "nccl": False, "multimem": True}[ARGS.collective]
+        self.hook = LatticeGradAllReduce(self.m, nr_buckets=buckets, policy=ARGS.bucket_policy, multimem=mm) \
+            if world > 1 else None
+        self.collective = None if self.hook is None else ("multimem" if self.hook._symm is not None else "nccl")
         self.launches_per_step = 2 if world == 1 else 1 + len(self.hook.buckets)
 
     def step(self, pos, grad_out):
@@ -328,7 +332,8 @@ def main():
         "config": {"workload": name, **{k: v for k, v in w.items()}, "points_per_gpu": n_local,
                    "timing": "inputs larger than L2 (features and their gradient are 48*4 B per point)",
                    "parallelism": f"dp{args.gpus}: points sharded, lattice replicated"
-                                  + (", bucketed all-reduce of the lattice gradient" if WORLD > 1 else "")},
+                                  + (f", all-reduce of the lattice gradient in {args.buckets} level bucket(s) "
+                                     f"({getattr(runner, 'collective', 'nccl')})" if WORLD > 1 else "")},
         "e2e": {"value": round(total / ms_e2e / 1e3, 2), "unit": "Mpoints/s", "h2d_bytes_per_step": n_local * d * 4,
                 "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e, 4),
                 "what": "every step: pinned host positions -> device (double-buffered, copied beside the previous step), module forward, MSE loss, backward, loss.item()"},

@@ -278,7 +278,8 @@ class EncodingWrapper:
         """(lattice_values_grad [L,C,2] | None, positions_grad [N,d] | None)
         (reference: Encoding<P,2>::backward).  ``lattice_grad_out`` lets the caller provide the
         buffer; ``level_begin/level_end`` restrict the levels (bucketed all-reduce overlap);
-        ``positions_grad_out`` is an existing position gradient to keep accumulating into."""
+        ``positions_grad_out`` is an existing position gradient to keep accumulating into;
+        ``zero=False`` accumulates onto a lattice gradient the caller has cleared itself."""
         self._check(inp)
         fp = self.fixed
         pos = inp.m_positions_raw
@@ -299,7 +300,8 @@ class EncodingWrapper:
                 pos_grad = positions_grad_out
                 flags |= PERMUTO_KEEP_POSITIONS_GRAD
             else:
-                pos_grad = torch.empty((n, fp.m_pos_dim), dtype=torch.float32, device=pos.device)
+                make = torch.empty if zero else torch.zeros  # without ZERO_OUTPUTS nothing clears it natively
+                pos_grad = make((n, fp.m_pos_dim), dtype=torch.float32, device=pos.device)
         lb = 0 if level_begin is None else int(level_begin)
         le = fp.m_nr_levels if level_end is None else int(level_end)
         with _guard(pos.device):

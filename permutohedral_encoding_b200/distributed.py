@@ -64,22 +64,67 @@ class LatticeGradAllReduce:
     level buckets and all-reduces each bucket while the next one is being computed.
 
     After ``loss.backward()`` the parameter's ``.grad`` holds the sum over ranks (or the mean
-    with ``average=True``).  Call ``remove()`` to restore single-GPU behaviour."""
+    with ``average=True``).  Call ``remove()`` to restore single-GPU behaviour.
 
-    def __init__(self, encoding, process_group=None, nr_buckets: int = 3, average: bool = False,
-                 policy: str = "halving"):
+    Collective used: with NCCL on GPUs that share an NVSwitch multicast domain the buckets are
+    reduced with ``multimem`` instructions (the switch adds the ranks' copies; PyTorch's
+    symmetric-memory all-reduce) on a side stream -- measured on 8 B200s 0.25 ms for the 96 MB
+    gradient against 0.32 ms for ``ncclAllReduce``, 0.055 against 0.097 ms for a 16 MB bucket;
+    otherwise (``multimem=False``, gloo, no multicast support) ``dist.all_reduce(async_op=True)``.
+    Constructing the hook is a collective call when ``multimem`` is not False: every rank of the
+    group must construct it."""
+
+    def __init__(self, encoding, process_group=None, nr_buckets: int = 2, average: bool = False,
+                 policy: str = "halving", multimem="auto"):
         self.encoding = encoding
         self.group = process_group
         self.average = average
         self.buckets = level_buckets(encoding.nr_levels, nr_buckets, policy)
+        self._symm = None
+        self._cleared = None
+        self.multimem_error = None
+        if multimem:
+            self._try_symmetric_memory(encoding.lattice_values, required=(multimem is True))
         encoding.lattice.backward_hook = self._backward
         self.last_works = []
+
+    def _try_symmetric_memory(self, values, required: bool) -> None:
+        group = self.group if self.group is not None else dist.group.WORLD
+        usable = values.is_cuda and dist.get_world_size(group) > 1 and dist.get_backend(group) == "nccl"
+        buf = None
+        if usable:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                buf = symm_mem.empty(values.numel(), dtype=torch.float32, device=values.device)
+                handle = symm_mem.rendezvous(buf, group)
+                if getattr(handle, "multicast_ptr", 1) == 0:  # no NVSwitch multicast object behind it
+                    self.multimem_error = "symmetric memory has no multicast pointer"
+                    buf = None
+            except Exception as exc:  # noqa: BLE001 -- any failure means "use the NCCL path"
+                self.multimem_error = repr(exc)
+                buf = None
+        if usable:
+            # every rank must take the same path: agree on the weakest outcome
+            flag = torch.tensor([1 if buf is not None else 0], device=values.device, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            if int(flag.item()) == 0:
+                buf = None
+        if buf is None and required:
+            raise RuntimeError("multimem all-reduce requested but symmetric memory with multicast is not available: "
+                               f"{self.multimem_error}")
+        if buf is not None:
+            self._symm = buf
+            self._group_name = group.group_name
+            self._comm_stream = torch.cuda.Stream(values.device)
 
     def remove(self) -> None:
         self.encoding.lattice.backward_hook = None
 
     def _backward(self, lattice, input_struct, grad_features):
-        lv_grad = torch.empty_like(input_struct.m_lattice_values)
+        values = input_struct.m_lattice_values
+        if self._symm is not None:
+            return self._backward_multimem(lattice, input_struct, grad_features, values)
+        lv_grad = torch.empty_like(values)
         pos_grad = None
         works = []
         for i, (l0, l1) in enumerate(self.buckets):
@@ -95,6 +140,42 @@ class LatticeGradAllReduce:
             lv_grad.div_(dist.get_world_size(self.group))
         self.last_works = works
         return lv_grad, pos_grad
+
+    def _backward_multimem(self, lattice, input_struct, grad_features, values):
+        """Buckets are computed on the caller's stream into a persistent symmetric buffer; a side
+        stream all-reduces each finished bucket in place, copies it into the tensor handed to
+        autograd (the buffer is overwritten by the next backward), beside the following bucket's
+        backward kernel.  Only the last bucket's all-reduce and copy are exposed.  The buffer is
+        cleared inside each bucket's backward call, right before its kernel: clearing it early (at
+        the end of the previous step) was measured 10 % slower end to end, because the memset is
+        also what brings the gradient slices into L2 ahead of the reductions."""
+        lv = self._symm.view(values.shape)          # same allocation on every rank
+        current = torch.cuda.current_stream(values.device)
+        comm = self._comm_stream
+        out = torch.empty_like(values)
+        out.record_stream(comm)
+        if self._cleared is not None:
+            current.wait_event(self._cleared)       # the previous step's copies out of the buffer
+        scale = 1.0 / dist.get_world_size(self.group) if self.average else None
+        pos_grad = None
+        for l0, l1 in self.buckets:
+            _, pg = lattice.backward(input_struct, grad_features, lattice_grad_out=lv, level_begin=l0,
+                                     level_end=l1, zero=True, positions_grad_out=pos_grad)
+            pos_grad = pg if pg is not None else pos_grad
+            ready = torch.cuda.Event()
+            ready.record(current)
+            comm.wait_event(ready)
+            with torch.cuda.stream(comm):
+                torch.ops.symm_mem.multimem_all_reduce_(lv[l0:l1].reshape(-1), "sum", self._group_name)
+                if scale is None:
+                    out[l0:l1].copy_(lv[l0:l1])
+                else:
+                    torch.mul(lv[l0:l1], scale, out=out[l0:l1])
+        done = torch.cuda.Event()
+        done.record(comm)
+        current.wait_event(done)
+        self._cleared = done
+        return out, pos_grad
 
 
 def all_reduce_bucketed(tensor_by_level: torch.Tensor, buckets, group=None) -> None:

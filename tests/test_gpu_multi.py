@@ -23,9 +23,9 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, use_multimem):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -49,7 +49,7 @@ def _worker(rank, world, port, out_dir):
     full_tg, full_pg = m.lattice_values.grad.clone(), pos.grad.clone()
     m.lattice_values.grad = None
     # this rank's shard with the bucketed all-reduce
-    hook = LatticeGradAllReduce(m, nr_buckets=3)
+    hook = LatticeGradAllReduce(m, nr_buckets=3, multimem=use_multimem)
     b, e = shard_bounds(n, rank, world)
     pos_s = pos_all[b:e].clone().requires_grad_(True)
     out_s = m(pos_s)
@@ -65,10 +65,11 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_sharded_step_matches_single_gpu(tmp_path):
+@pytest.mark.parametrize("use_multimem", [False, "auto"])
+def test_sharded_step_matches_single_gpu(tmp_path, use_multimem):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     port = _free_port()
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), use_multimem), nprocs=2, join=True)
     for r in range(2):
         assert torch.load(tmp_path / f"r{r}.pt")["ok"] == (True, True, True)
