@@ -230,7 +230,7 @@ def max_over_ranks(x, device):
     return t.item()
 
 
-def cpu_baseline(w, n_sample_hint=None):
+def cpu_baseline(w):
     """The C restatement (oracle/) on the host cores: forward + backward into the table on a
     bounded sample of the same workload."""
     from oracle import permuto_oracle as po
@@ -252,14 +252,17 @@ def cpu_baseline(w, n_sample_hint=None):
         po.backward(pos, table, scale, shift, anneal, go, need_table=True, need_pos=False)
         return time.perf_counter() - t0
 
-    n0 = 2 ** 14
-    t = run(n0)
-    n = n_sample_hint or int(min(w["total_points"], max(n0, n0 * (10.0 / max(t, 1e-3)))))
-    n = 1 << (n.bit_length() - 1)
-    t = run(n)
-    return {"value": round(n / t / 1e6, 4), "unit": "Mpoints/s", "cores": cores, "kind": "port",
-            "sample": f"forward+backward of {n} points of the same workload, OpenMP over {cores} host threads, "
-                      f"{t:.1f} s"}
+    n = int(min(w["total_points"], 2 ** 20))
+    run(2 ** 12)  # page in the table, start the thread pool
+    elapsed, points, reps = 0.0, 0, 0
+    budget = float(os.environ.get("PERMUTO_CPU_BASELINE_SECONDS", "10"))
+    while elapsed < budget and reps < 64:
+        elapsed += run(n)
+        points += n
+        reps += 1
+    return {"value": round(points / elapsed / 1e6, 4), "unit": "Mpoints/s", "cores": cores, "kind": "port",
+            "sample": f"{reps} x forward+backward of {n} points of the same workload (C restatement in oracle/, "
+                      f"OpenMP over {cores} host threads), {elapsed:.1f} s"}
 
 
 def main():
@@ -349,6 +352,10 @@ def main():
                        "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e, 4)}
     else:
         line["gpu_launches"] = runner.launches_per_step * args.steps
+        with torch.no_grad():
+            ms_fo = max_over_ranks(timed(lambda: runner.m(pos), max(5, min(args.steps, 30)), 3, sync), device)
+        line["forward_only"] = {"value": round(total / ms_fo / 1e3, 2), "unit": "Mpoints/s", "ms_per_step": round(ms_fo, 4),
+                                "what": "module forward alone, inputs resident"}
         # kernel-only durations on the launching stream, for the roofline of the dominant kernel
         fwd, bwd = runner.kernels(pos, grad_out)
         ms_f = timed(fwd, 20, 3, torch.cuda.synchronize)

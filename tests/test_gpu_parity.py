@@ -370,3 +370,38 @@ def test_host_point_feeder_keeps_batches_apart(nat):
     assert [float(s) for s in sums] == [float(i) * 4096 * 3 for i in range(6)]
     with pytest.raises(RuntimeError):
         feeder.next()
+
+
+def test_training_step_can_be_replayed_from_a_cuda_graph(nat):
+    """Nothing on the path synchronises or allocates outside the caller's allocator, so a whole
+    forward + backward can be captured once and replayed (small batches are launch-bound)."""
+    name = "window_d3"
+    c, inp = cases.CASES[name], cases.make_inputs(name)
+    m = build_module(c, inp)
+    pos = T(inp["positions"])
+    go = T(inp["grad_out"])
+    static_pos = pos.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):          # warm-up outside capture, as torch.cuda.graph requires
+        for _ in range(3):
+            m.lattice_values.grad = None
+            m(static_pos).backward(go)
+    torch.cuda.current_stream().wait_stream(side)
+    m.lattice_values.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = m(static_pos)
+        out.backward(go)
+    want_out = m(pos).detach().clone()
+    m.lattice_values.grad = None
+    m(pos).backward(go)
+    want_grad = m.lattice_values.grad.clone()
+    static_pos.copy_(pos * 0.5)
+    graph.replay()
+    static_pos.copy_(pos)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want_out)
+    lvl = want_grad.abs().amax(dim=(1, 2), keepdim=True)
+    assert torch.all((m.lattice_values.grad - want_grad).abs() <= BWD_RTOL * lvl + 1e-12)
