@@ -243,10 +243,15 @@ __global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) backward_kernel(
     for (int i = 0; i < D; ++i) dpos[i] = 0.f;
     bool probe = a.aggregate != 0;
 
+    // the next group's 32 bytes of the gradient row are requested before this group is worked on
+    float g_next[2 * LPT];
+    load_row_segment<LPT>(p, a.grad_features, n, pass_begin, g_next);
 #pragma unroll 1
     for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
     float g[2 * LPT];
-    load_row_segment<LPT>(p, a.grad_features, n, l0, g);
+#pragma unroll
+    for (int i = 0; i < 2 * LPT; ++i) g[i] = g_next[i];
+    if (l0 + LPT < pass_end) load_row_segment<LPT>(p, a.grad_features, n, l0 + LPT, g_next);
 #pragma unroll
     for (int k = 0; k < LPT; ++k) {
         const int l = l0 + k;
