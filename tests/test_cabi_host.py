@@ -69,6 +69,11 @@ def test_argument_validation_without_gpu(nat):
     ins0 = nat.PermutoInputs(0, 8, 3, 1, 8, 8, 8, 8)
     assert lib.permuto_forward(C.byref(cfg), C.byref(ins0), C.c_void_p(8), None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
     assert "0 points" in nat.last_error()
+    big = nat.PermutoInputs(2 ** 31, 8, 3, 1, 8, 8, 8, 8)
+    assert lib.permuto_forward(C.byref(cfg), C.byref(big), C.c_void_p(8), None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
+    assert "2^31" in nat.last_error()
+    odd = nat.PermutoInputs(10, 8, 3, 1, 12, 8, 8, 8)   # lattice_values not 8-byte aligned
+    assert lib.permuto_forward(C.byref(cfg), C.byref(odd), C.c_void_p(8), None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
     assert lib.permuto_backward(C.byref(cfg), C.byref(ins), C.c_void_p(8), None, None, 2, 9, 0, None) \
         == nat.PERMUTO_ERR_INVALID_ARGUMENT
     assert "level range" in nat.last_error()

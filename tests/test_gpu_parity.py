@@ -405,3 +405,45 @@ def test_training_step_can_be_replayed_from_a_cuda_graph(nat):
     assert torch.equal(out, want_out)
     lvl = want_grad.abs().amax(dim=(1, 2), keepdim=True)
     assert torch.all((m.lattice_values.grad - want_grad).abs() <= BWD_RTOL * lvl + 1e-12)
+
+
+@pytest.mark.parametrize("what", ["identical_points", "huge_coordinates", "capacity_one", "one_level", "negative_box"])
+def test_edge_inputs_against_oracle(nat, oracle, what):
+    """Inputs at the edges of the domain: every lane of a warp in the same simplex (maximal
+    collision merging), coordinates so large that the products of the rounding step stop being
+    exact (the kernels then take the reference's own ceil expression), a one-slot table, a single
+    level, negative coordinates."""
+    c = dict(pos_dim=3, capacity=2 ** 12, nr_levels=8, sigma=(1.0, 1e-3), n=1000, box=(0.0, 1.0), table=1.0)
+    if what == "capacity_one":
+        c["capacity"] = 1
+    if what == "one_level":
+        c["nr_levels"] = 1
+    if what == "negative_box":
+        c["box"] = (-50.0, -49.0)
+    name = "edge_" + what
+    cases.CASES[name] = c
+    try:
+        inp = cases.make_inputs(name)
+    finally:
+        del cases.CASES[name]
+    if what == "identical_points":
+        inp["positions"][:] = inp["positions"][0]
+    if what == "huge_coordinates":
+        inp["positions"] = (inp["positions"] * 2.0e4 - 1.0e4).astype(np.float32)   # elevated up to ~1e7
+        scale = oracle.scale_factor(inp["sigmas"], 3)
+        assert np.abs(inp["positions"]).max() * scale.max() > 4194304.0
+    # with a single slot every vertex reads the same value, so the grad-grad features are
+    # value * sum(dB) = value * 0: pure cancellation noise on both sides, nothing to compare
+    parts = ("forward", "backward") if what == "capacity_one" else ("forward", "backward", "double")
+    check_all(nat, oracle, c, inp, parts=parts)
+
+
+def test_many_dimensions_non_power_of_two_levels(nat, oracle):
+    """pos_dim 5 (d+1 = 6: rank wrap without the power-of-two mask), 7 levels, odd point count."""
+    c = dict(pos_dim=5, capacity=3001, nr_levels=7, sigma=(2.0, 5e-2), n=777, box=(-2.0, 2.0), table=1.0)
+    cases.CASES["edge_d5"] = c
+    try:
+        inp = cases.make_inputs("edge_d5")
+    finally:
+        del cases.CASES["edge_d5"]
+    check_all(nat, oracle, c, inp)
