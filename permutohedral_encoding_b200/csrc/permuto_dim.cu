@@ -341,10 +341,16 @@ __global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) double_backward_
     for (int i = 0; i < D; ++i) dpg[i] = __ldg(a.double_positions_grad + n * D + i);
     bool probe = a.aggregate != 0;  // as in backward_kernel
 
+    float g_next[2 * LPT];  // as in backward_kernel: the next group's gradient segment is requested early
+    if (TABLE) load_row_segment<LPT>(p, a.grad_features, n, pass_begin, g_next);
 #pragma unroll 1
     for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
     float g[2 * LPT];
-    if (TABLE) load_row_segment<LPT>(p, a.grad_features, n, l0, g);
+    if (TABLE) {
+#pragma unroll
+        for (int i = 0; i < 2 * LPT; ++i) g[i] = g_next[i];
+        if (l0 + LPT < pass_end) load_row_segment<LPT>(p, a.grad_features, n, l0 + LPT, g_next);
+    }
     float out[2 * LPT];
 #pragma unroll
     for (int k = 0; k < LPT; ++k) {
