@@ -117,3 +117,30 @@ def test_module_needs_cuda_and_has_no_cpu_fallback():
     from permutohedral_encoding_b200 import PermutoEncoding
     with pytest.raises((RuntimeError, AssertionError)):
         PermutoEncoding(3, 1024, 4, 2, np.geomspace(1, 0.1, 4))
+
+
+def test_header_is_plain_c_and_library_links_from_c(tmp_path, nat):
+    """The boundary is a C ABI: the header compiles as C99, and a C program linked against the
+    library can call the host-side entry points (no GPU needed for these)."""
+    import subprocess
+    src = tmp_path / "use_abi.c"
+    src.write_text(
+        '#include <stdio.h>\n#include "permuto_b200.h"\n'
+        "int main(void) {\n"
+        "  double sig[2] = {1.0, 0.5}; float out[6];\n"
+        "  if (permuto_abi_version() != PERMUTO_ABI_VERSION) return 1;\n"
+        "  if (permuto_scale_factor(sig, 2, 3, out) != PERMUTO_OK) return 2;\n"
+        "  if (permuto_scale_factor(sig, 2, 9, out) != PERMUTO_ERR_UNSUPPORTED) return 3;\n"
+        "  if (permuto_forward(NULL, NULL, NULL, NULL) != PERMUTO_ERR_INVALID_ARGUMENT) return 4;\n"
+        '  printf("%.9g %.9g %s\\n", out[0], out[5], permuto_last_error());\n'
+        "  return 0;\n}\n")
+    exe = tmp_path / "use_abi"
+    lib_dir = os.path.dirname(nat.LIB_PATH)
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", lib_dir, "-l:libpermuto_b200.so", f"-Wl,-rpath,{lib_dir}"], check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    a, b = res.stdout.split()[:2]
+    want = nat.scale_factor([1.0, 0.5], 3)
+    assert np.float32(a) == want[0, 0] and np.float32(b) == want[1, 2]
+    assert "NULL" in res.stdout
