@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "train", "sharded"])
+    ap.add_argument("--workload", default=None, choices=[None, "train", "sharded", "train_f8"])
     ap.add_argument("--buckets", type=int, default=2, help="level buckets of the overlapped all-reduce")
     ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "multimem"])
     ap.add_argument("--bucket-policy", default="halving", choices=["halving", "even"])
@@ -68,6 +68,9 @@ import torch.distributed as dist  # noqa: E402
 WORKLOADS = {
     "train": dict(pos_dim=3, nr_levels=24, capacity=2 ** 18, total_points=2 ** 20, sigma=(1.0, 1e-4)),
     "sharded": dict(pos_dim=3, nr_levels=24, capacity=2 ** 19, total_points=2 ** 24, sigma=(1.0, 1e-4)),
+    # not a reference configuration (it has no 8-feature levels): the same 48 outputs from 6 levels of
+    # 8 features, every table access a whole 32-byte sector
+    "train_f8": dict(pos_dim=3, nr_levels=6, nr_feat=8, capacity=2 ** 18, total_points=2 ** 20, sigma=(1.0, 1e-4)),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch on the "train" workload, from the ncu
@@ -125,7 +128,7 @@ class ClockSampler:
 def make_data(w, n_local, seed, device):
     d, L, cap = w["pos_dim"], w["nr_levels"], w["capacity"]
     gen = torch.Generator(device="cpu").manual_seed(1234)  # lattice and shift identical on every rank
-    table = ((torch.rand((L, cap, 2), generator=gen) * 2 - 1) * 1e-4)
+    table = ((torch.rand((L, cap, w.get("nr_feat", 2)), generator=gen) * 2 - 1) * 1e-4)
     shift = torch.randn((L, d), generator=gen) * 10
     gen = torch.Generator(device="cpu").manual_seed(seed)
     pos_host = torch.rand((n_local, d), generator=gen).pin_memory()
@@ -144,7 +147,7 @@ class OursStep:
         from permutohedral_encoding_b200 import PermutoEncoding
         from permutohedral_encoding_b200.distributed import LatticeGradAllReduce
         sig = np.geomspace(w["sigma"][0], w["sigma"][1], w["nr_levels"])
-        self.m = PermutoEncoding(w["pos_dim"], w["capacity"], w["nr_levels"], 2, sig)
+        self.m = PermutoEncoding(w["pos_dim"], w["capacity"], w["nr_levels"], w.get("nr_feat", 2), sig)
         with torch.no_grad():
             self.m.lattice_values.copy_(table)
             self.m.random_shift_per_level.copy_(shift)
@@ -237,7 +240,8 @@ def cpu_baseline(w):
     d, L, cap = w["pos_dim"], w["nr_levels"], w["capacity"]
     sig = np.geomspace(w["sigma"][0], w["sigma"][1], L)
     rng = np.random.default_rng(0)
-    table = (rng.random((L, cap, 2), dtype=np.float32) * 2 - 1) * np.float32(1e-4)
+    F = w.get("nr_feat", 2)
+    table = (rng.random((L, cap, F), dtype=np.float32) * 2 - 1) * np.float32(1e-4)
     shift = (rng.standard_normal((L, d)) * 10).astype(np.float32)
     scale = po.scale_factor(sig, d)
     anneal = np.ones(L, np.float32)
@@ -246,7 +250,7 @@ def cpu_baseline(w):
 
     def run(n):
         pos = rng.random((n, d), dtype=np.float32)
-        go = rng.standard_normal((n, 2 * L)).astype(np.float32)
+        go = rng.standard_normal((n, F * L)).astype(np.float32)
         t0 = time.perf_counter()
         po.forward(pos, table, scale, shift, anneal)
         po.backward(pos, table, scale, shift, anneal, go, need_table=True, need_pos=False)
@@ -271,6 +275,10 @@ def main():
     w = WORKLOADS[name]
     d, L, cap = w["pos_dim"], w["nr_levels"], w["capacity"]
     use_ref_ext = False
+    if args.impl == "reference" and w.get("nr_feat", 2) != 2:
+        if RANK == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference implements nr_feat_per_level == 2 only"}))
+        return 0
     if args.impl == "reference":
         from oracle import ref_shim
         use_ref_ext = ref_shim.available() and torch.cuda.is_available()
@@ -303,7 +311,8 @@ def main():
     n_local = e - b
     table, shift, pos_host = make_data(w, n_local, 100 + RANK, device)
     pos = pos_host.to(device)
-    grad_out = device_randn((n_local, 2 * L), 200 + RANK, device)
+    F = w.get("nr_feat", 2)
+    grad_out = device_randn((n_local, F * L), 200 + RANK, device)
     target = torch.full((1, 1), 0.3, device=device)
 
     if args.impl == "reference":
@@ -361,8 +370,8 @@ def main():
         ms_f = timed(fwd, 20, 3, torch.cuda.synchronize)
         ms_b = timed(bwd, 20, 3, torch.cuda.synchronize)  # includes the memset of the gradient slices
         V = d + 1
-        bytes_f = n_local * (4 * d + 4 * L * V * 2 + 4 * L * 2)
-        bytes_b = n_local * (4 * d + 4 * L * 2 + 4 * L * V * 2) + 4 * L * cap * 2
+        bytes_f = n_local * (4 * d + 4 * L * V * F + 4 * L * F)
+        bytes_b = n_local * (4 * d + 4 * L * F + 4 * L * V * F) + 4 * L * cap * F
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))

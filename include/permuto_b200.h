@@ -11,14 +11,14 @@
  *
  * Layouts (all fp32, element strides):
  *   positions            [N, pos_dim]      arbitrary strides (pos_stride_n, pos_stride_d)
- *   lattice_values       [L, capacity, 2]  contiguous (the reference parameter layout)
+ *   lattice_values       [L, capacity, F]  contiguous (the reference parameter layout), F = nr_feat_per_level
  *   scale_factor         [L, pos_dim]      contiguous, from permuto_scale_factor()
  *   random_shift         [L, pos_dim]      contiguous
  *   anneal_window        [L]               contiguous
- *   features / gradients [N, W]            contiguous, W = 2*(L + extra_levels), column
- *                                          2*level + feature -- the ordering the reference
+ *   features / gradients [N, W]            contiguous, W = F*(L + extra_levels), column
+ *                                          F*level + feature -- the ordering the reference
  *                                          module returns (src/pytorch_modules/modules.py:87)
- *   lattice_grad         [L, capacity, 2]  contiguous, the parameter's own layout
+ *   lattice_grad         [L, capacity, F]  contiguous, the parameter's own layout
  *   positions_grad       [N, pos_dim]      contiguous
  *
  * Every function returns PERMUTO_OK or a negative status; permuto_last_error() gives the
@@ -38,7 +38,7 @@ extern "C" {
 enum {
     PERMUTO_OK = 0,
     PERMUTO_ERR_INVALID_ARGUMENT = -1, /* NULL pointer, bad size or stride                    */
-    PERMUTO_ERR_UNSUPPORTED = -2,      /* pos_dim outside 2..7 or nr_feat_per_level != 2      */
+    PERMUTO_ERR_UNSUPPORTED = -2,      /* pos_dim outside 2..7 or nr_feat_per_level not 2/4/8 */
     PERMUTO_ERR_CUDA = -3              /* a CUDA runtime call or kernel launch failed         */
 };
 
@@ -47,13 +47,14 @@ enum {
  * per call. */
 typedef struct permuto_config {
     int32_t pos_dim;           /* 2..7 (Encoding.cuh:138-157)                                 */
-    int32_t nr_feat_per_level; /* must be 2 (Encoding.cuh:140-143)                            */
+    int32_t nr_feat_per_level; /* 2 (the reference's only width, Encoding.cuh:140-143), or 4 / 8,
+                                  which the reference lists as not yet implemented            */
     int32_t nr_levels;         /* L >= 1                                                      */
     int32_t capacity;          /* slots per level, any value >= 1 (power of two is faster)    */
     int32_t concat_points;     /* 0/1: append ceil(pos_dim/2) levels holding the raw points   */
     float points_scaling;      /* factor applied to the concatenated points                   */
     int32_t levels_per_pass;   /* scheduling hint: levels one sweep over the points handles, a
-                                  multiple of 4; 0 = chosen from the capacity (no reference
+                                  multiple of 8/F; 0 = chosen from the capacity (no reference
                                   counterpart; results do not depend on it)                    */
 } permuto_config;
 
@@ -80,9 +81,9 @@ enum {
 int permuto_abi_version(void);
 const char *permuto_last_error(void);
 
-/* Number of extra output levels when concat_points is set: ceil(pos_dim / 2)
+/* Number of extra output levels when concat_points is set: ceil(pos_dim / nr_feat_per_level)
  * (src/Encoding.cu:71-74). */
-int permuto_extra_levels(int32_t pos_dim, int32_t concat_points);
+int permuto_extra_levels(int32_t pos_dim, int32_t nr_feat_per_level, int32_t concat_points);
 
 /* Host computation of scale_factor[L, pos_dim] (host pointer out).  Replaces
  * EncodingFixedParams::compute_scale_factor_tensor (Encoding.cuh:55-69) and reproduces its
@@ -106,7 +107,7 @@ int permuto_backward(const permuto_config *cfg, const permuto_inputs *in, const 
  * Encoding<P,2>::double_backward_from_positions (src/Encoding.cu:218-334).
  * double_positions_grad [N, pos_dim] contiguous = d loss / d positions_grad;
  * grad_features [N, W] = the upstream gradient the first backward received.
- * Outputs (each may be NULL): lattice_grad [L, capacity, 2]; grad_grad_features [N, W]
+ * Outputs (each may be NULL): lattice_grad [L, capacity, F]; grad_grad_features [N, W]
  * (= d loss / d grad_features; the concat columns are written as zero). */
 int permuto_double_backward(const permuto_config *cfg, const permuto_inputs *in,
                             const float *double_positions_grad, const float *grad_features,

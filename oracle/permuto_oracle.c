@@ -25,7 +25,14 @@
 #include <string.h>
 
 #define PERMUTO_MAX_DIM 7
-#define NFEAT 2
+#define MAX_FEAT 8
+/* Features per level.  2 is the only width the reference implements (Encoding.cuh:140-143);
+ * 4 and 8 follow the same arithmetic with wider table entries and are pinned by the identities
+ * in the tests only (the reference cannot produce fixtures for them).  Set per call by the
+ * Python front end from the table's last dimension. */
+static int g_nfeat = 2;
+#define NFEAT g_nfeat
+void permuto_oracle_set_nfeat(int nfeat) { g_nfeat = nfeat; }
 
 /* How nvcc's default -fmad=true contracts the reference's elevate loop
  * (EncodingGPU.cuh:130-138; cf_i = t_i*scale_i with t_i = pos_i + shift_i).  Determined by
@@ -216,16 +223,15 @@ void permuto_oracle_forward(int pos_dim, int nr_levels, int capacity, int64_t n_
             locate_simplex(d, pos, shift + l * d, scale + l * d, &s);
             const float *tl = table + (int64_t)l * capacity * NFEAT;
             float w_lvl = anneal[l];
-            float ax = 0.0f, ay = 0.0f;
+            float acc_f[MAX_FEAT] = {0};
             for (int r = 0; r < V; r++) {
                 vertex_key(d, &s, r, key);
                 int slot = hash_slot(key, d, capacity);
                 float w = s.bary[r] * w_lvl;
-                ax = fmaf(tl[slot * NFEAT + 0], w, ax); /* :246-247, contracted by -fmad */
-                ay = fmaf(tl[slot * NFEAT + 1], w, ay);
+                for (int f = 0; f < NFEAT; f++) /* :246-247, contracted by -fmad */
+                    acc_f[f] = fmaf(tl[slot * NFEAT + f], w, acc_f[f]);
             }
-            o[l * NFEAT + 0] = ax;
-            o[l * NFEAT + 1] = ay;
+            for (int f = 0; f < NFEAT; f++) o[l * NFEAT + f] = acc_f[f];
         }
         /* :105-121 concat rows */
         for (int e = 0; e < extra; e++)
@@ -265,18 +271,15 @@ void permuto_oracle_backward(int pos_dim, int nr_levels, int capacity, int64_t n
             float w_lvl = anneal[l];
             for (int64_t n = 0; n < n_pos; n++) {
                 locate_simplex(d, row(positions, n, d), shift + l * d, scale + l * d, &s);
-                float gx = grad_out[n * width + l * NFEAT + 0];
-                float gy = grad_out[n * width + l * NFEAT + 1];
+                const float *gl = grad_out + n * width + l * NFEAT;
                 for (int r = 0; r < V; r++) {
                     vertex_key(d, &s, r, key);
                     int slot = hash_slot(key, d, capacity);
                     float w = s.bary[r] * w_lvl;
-                    float ax = gx * w, ay = gy * w;
-                    acc[slot * NFEAT + 0] += (double)ax;
-                    acc[slot * NFEAT + 1] += (double)ay;
-                    if (aabs) {
-                        aabs[slot * NFEAT + 0] += fabs((double)ax);
-                        aabs[slot * NFEAT + 1] += fabs((double)ay);
+                    for (int f = 0; f < NFEAT; f++) {
+                        float af = gl[f] * w;
+                        acc[slot * NFEAT + f] += (double)af;
+                        if (aabs) aabs[slot * NFEAT + f] += fabs((double)af);
                     }
                 }
             }
@@ -299,15 +302,13 @@ void permuto_oracle_backward(int pos_dim, int nr_levels, int capacity, int64_t n
                 locate_simplex(d, row(positions, n, d), shift + l * d, sc, &s);
                 const float *tl = table + (int64_t)l * slice;
                 float w_lvl = anneal[l];
-                float gx = grad_out[n * width + l * NFEAT + 0];
-                float gy = grad_out[n * width + l * NFEAT + 1];
+                const float *gl = grad_out + n * width + l * NFEAT;
                 float dB[PERMUTO_MAX_DIM + 2];
                 for (int r = 0; r <= d + 1; r++) dB[r] = 0.0f;
                 for (int r = 0; r < V; r++) {
                     vertex_key(d, &s, r, key);
                     int slot = hash_slot(key, d, capacity);
-                    dB[r] += tl[slot * NFEAT + 0] * w_lvl * gx; /* :688-689 */
-                    dB[r] += tl[slot * NFEAT + 1] * w_lvl * gy;
+                    for (int f = 0; f < NFEAT; f++) dB[r] += tl[slot * NFEAT + f] * w_lvl * gl[f]; /* :688-689 */
                 }
                 dB[d + 1] += dB[0]; /* :698 */
                 float dE[PERMUTO_MAX_DIM + 1];
@@ -376,18 +377,14 @@ void permuto_oracle_double_backward(int pos_dim, int nr_levels, int capacity, in
                 locate_simplex(d, row(positions, n, d), shift + l * d, sc, &s);
                 float dB[PERMUTO_MAX_DIM + 2];
                 DOUBLE_BACK_DB(dB, s, sc, dpg + n * d);
-                float gx = grad_out[n * width + l * NFEAT + 0];
-                float gy = grad_out[n * width + l * NFEAT + 1];
+                const float *gl = grad_out + n * width + l * NFEAT;
                 for (int r = 0; r < V; r++) {
                     vertex_key(d, &s, r, key);
                     int slot = hash_slot(key, d, capacity);
-                    float ax = dB[r] * w_lvl * gx; /* :1244-1245 */
-                    float ay = dB[r] * w_lvl * gy;
-                    acc[slot * NFEAT + 0] += (double)ax;
-                    acc[slot * NFEAT + 1] += (double)ay;
-                    if (aabs) {
-                        aabs[slot * NFEAT + 0] += fabs((double)ax);
-                        aabs[slot * NFEAT + 1] += fabs((double)ay);
+                    for (int f = 0; f < NFEAT; f++) {
+                        float af = dB[r] * w_lvl * gl[f]; /* :1244-1245 */
+                        acc[slot * NFEAT + f] += (double)af;
+                        if (aabs) aabs[slot * NFEAT + f] += fabs((double)af);
                     }
                 }
             }
@@ -412,15 +409,13 @@ void permuto_oracle_double_backward(int pos_dim, int nr_levels, int capacity, in
                 float w_lvl = anneal[l];
                 float dB[PERMUTO_MAX_DIM + 2];
                 DOUBLE_BACK_DB(dB, s, sc, dpg + n * d);
-                float ax = 0.0f, ay = 0.0f;
+                float acc_f[MAX_FEAT] = {0};
                 for (int r = 0; r < V; r++) {
                     vertex_key(d, &s, r, key);
                     int slot = hash_slot(key, d, capacity);
-                    ax += dB[r] * w_lvl * tl[slot * NFEAT + 0]; /* :1484-1485 */
-                    ay += dB[r] * w_lvl * tl[slot * NFEAT + 1];
+                    for (int f = 0; f < NFEAT; f++) acc_f[f] += dB[r] * w_lvl * tl[slot * NFEAT + f]; /* :1484-1485 */
                 }
-                o[l * NFEAT + 0] = ax;
-                o[l * NFEAT + 1] = ay;
+                for (int f = 0; f < NFEAT; f++) o[l * NFEAT + f] = acc_f[f];
             }
             for (int e = 0; e < extra * NFEAT; e++) o[nr_levels * NFEAT + e] = 0.0f;
         }

@@ -68,7 +68,8 @@ def max_threads() -> int:
     return int(lib().permuto_oracle_max_threads())
 
 
-def extra_levels(pos_dim: int, concat_points: bool) -> int:
+def extra_levels(pos_dim: int, concat_points: bool, nr_feat: int = 2) -> int:
+    lib().permuto_oracle_set_nfeat(int(nr_feat))
     return int(lib().permuto_oracle_extra_levels(int(pos_dim), int(bool(concat_points))))
 
 
@@ -88,9 +89,10 @@ def _common(positions, table, scale, shift, anneal):
     anneal, ap = _f(anneal)
     n, d = positions.shape
     nl, cap, nf = table.shape
-    assert nf == 2 and scale.shape == (nl, d) and shift.shape == (nl, d) and anneal.shape == (nl,)
+    assert nf in (2, 4, 8) and scale.shape == (nl, d) and shift.shape == (nl, d) and anneal.shape == (nl,)
+    lib().permuto_oracle_set_nfeat(int(nf))
     keep = (positions, table, scale, shift, anneal)
-    return keep, (n, d, nl, cap), (pp, tp, sp, hp, ap)
+    return keep, (n, d, nl, cap, nf), (pp, tp, sp, hp, ap)
 
 
 def lattice(positions, scale, shift, capacity: int, want=("keys", "slots", "bary", "rank")):
@@ -111,9 +113,9 @@ def lattice(positions, scale, shift, capacity: int, want=("keys", "slots", "bary
 
 
 def forward(positions, table, scale, shift, anneal, concat_points=False, points_scaling=1.0):
-    keep, (n, d, nl, cap), (pp, tp, sp, hp, ap) = _common(positions, table, scale, shift, anneal)
-    extra = extra_levels(d, concat_points)
-    out = np.empty((n, (nl + extra) * 2), np.float32)
+    keep, (n, d, nl, cap, nf), (pp, tp, sp, hp, ap) = _common(positions, table, scale, shift, anneal)
+    extra = extra_levels(d, concat_points, nf)
+    out = np.empty((n, (nl + extra) * nf), np.float32)
     lib().permuto_oracle_forward(C.c_int(d), C.c_int(nl), C.c_int(cap), C.c_int64(n), pp, tp, sp,
                                  hp, ap, C.c_int(int(concat_points)), C.c_float(points_scaling),
                                  out.ctypes.data_as(_f32p))
@@ -122,12 +124,12 @@ def forward(positions, table, scale, shift, anneal, concat_points=False, points_
 
 def backward(positions, table, scale, shift, anneal, grad_out, concat_points=False,
              need_table=True, need_pos=False, need_abs=False):
-    keep, (n, d, nl, cap), (pp, tp, sp, hp, ap) = _common(positions, table, scale, shift, anneal)
-    extra = extra_levels(d, concat_points)
+    keep, (n, d, nl, cap, nf), (pp, tp, sp, hp, ap) = _common(positions, table, scale, shift, anneal)
+    extra = extra_levels(d, concat_points, nf)
     grad_out, gp = _f(grad_out)
-    assert grad_out.shape == (n, (nl + extra) * 2)
-    tg = np.empty((nl, cap, 2), np.float32) if need_table else None
-    ta = np.empty((nl, cap, 2), np.float32) if (need_table and need_abs) else None
+    assert grad_out.shape == (n, (nl + extra) * nf)
+    tg = np.empty((nl, cap, nf), np.float32) if need_table else None
+    ta = np.empty((nl, cap, nf), np.float32) if (need_table and need_abs) else None
     pg = np.empty((n, d), np.float32) if need_pos else None
     lib().permuto_oracle_backward(C.c_int(d), C.c_int(nl), C.c_int(cap), C.c_int64(n), pp, tp, sp,
                                   hp, ap, C.c_int(int(concat_points)), gp, _opt(tg, _f32p),
@@ -137,14 +139,14 @@ def backward(positions, table, scale, shift, anneal, grad_out, concat_points=Fal
 
 def double_backward(positions, table, scale, shift, anneal, dpg, grad_out, concat_points=False,
                     need_table=True, need_ggo=True, need_abs=False):
-    keep, (n, d, nl, cap), (pp, tp, sp, hp, ap) = _common(positions, table, scale, shift, anneal)
-    extra = extra_levels(d, concat_points)
+    keep, (n, d, nl, cap, nf), (pp, tp, sp, hp, ap) = _common(positions, table, scale, shift, anneal)
+    extra = extra_levels(d, concat_points, nf)
     grad_out, gp = _f(grad_out)
     dpg, dp = _f(dpg)
-    assert grad_out.shape == (n, (nl + extra) * 2) and dpg.shape == (n, d)
-    tg = np.empty((nl, cap, 2), np.float32) if need_table else None
-    ta = np.empty((nl, cap, 2), np.float32) if (need_table and need_abs) else None
-    gg = np.empty((n, (nl + extra) * 2), np.float32) if need_ggo else None
+    assert grad_out.shape == (n, (nl + extra) * nf) and dpg.shape == (n, d)
+    tg = np.empty((nl, cap, nf), np.float32) if need_table else None
+    ta = np.empty((nl, cap, nf), np.float32) if (need_table and need_abs) else None
+    gg = np.empty((n, (nl + extra) * nf), np.float32) if need_ggo else None
     lib().permuto_oracle_double_backward(C.c_int(d), C.c_int(nl), C.c_int(cap), C.c_int64(n), pp,
                                          tp, sp, hp, ap, C.c_int(int(concat_points)), dp, gp,
                                          _opt(tg, _f32p), _opt(ta, _f32p), _opt(gg, _f32p))

@@ -60,7 +60,7 @@ def _load() -> C.CDLL:
     lib.permuto_abi_version.restype = C.c_int
     lib.permuto_last_error.restype = C.c_char_p
     lib.permuto_extra_levels.restype = C.c_int
-    lib.permuto_extra_levels.argtypes = [C.c_int32, C.c_int32]
+    lib.permuto_extra_levels.argtypes = [C.c_int32, C.c_int32, C.c_int32]
     lib.permuto_scale_factor.restype = C.c_int
     lib.permuto_scale_factor.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     cfgp, inp = C.POINTER(PermutoConfig), C.POINTER(PermutoInputs)
@@ -100,8 +100,8 @@ def scale_factor(sigmas, pos_dim: int) -> np.ndarray:
     return out
 
 
-def extra_levels(pos_dim: int, concat_points: bool) -> int:
-    return int(lib.permuto_extra_levels(int(pos_dim), int(bool(concat_points))))
+def extra_levels(pos_dim: int, concat_points: bool, nr_feat_per_level: int = 2) -> int:
+    return int(lib.permuto_extra_levels(int(pos_dim), int(nr_feat_per_level), int(bool(concat_points))))
 
 
 def _ptr(t):
@@ -198,12 +198,13 @@ class EncodingWrapper:
     def __init__(self, pos_dim, nr_feat_per_level, fixed_params: EncodingFixedParams):
         if int(pos_dim) not in (2, 3, 4, 5, 6, 7):
             raise RuntimeError("Encoding: pos_dim must be 2,3,4,5,6 or 7")
-        if int(nr_feat_per_level) != 2:
-            raise RuntimeError(
-                "Encoding: nr_feat_per_level must be 2 since other values are not yet implemented")
+        if int(nr_feat_per_level) not in (2, 4, 8):
+            raise RuntimeError("Encoding: nr_feat_per_level must be 2, 4 or 8")
         self.fixed = fixed_params
         self.aggregate_collisions = True
-        self._width = 2 * (fixed_params.m_nr_levels + extra_levels(fixed_params.m_pos_dim, fixed_params.m_concat_points))
+        self._feat = int(nr_feat_per_level)
+        self._width = self._feat * (fixed_params.m_nr_levels + extra_levels(
+            fixed_params.m_pos_dim, fixed_params.m_concat_points, self._feat))
 
     @staticmethod
     def create(pos_dim, nr_feat_per_level, fixed_params) -> "EncodingWrapper":
@@ -224,8 +225,8 @@ class EncodingWrapper:
         if pos.shape[1] != fp.m_pos_dim:
             raise RuntimeError("Pos dim for the lattice doesn't correspond with the position of the points. "
                                f"Lattice was initialized with {fp.m_pos_dim} and points have pos dim {pos.shape[1]}")
-        if lv.dim() != 3 or tuple(lv.shape) != (fp.m_nr_levels, fp.m_capacity, 2):
-            raise RuntimeError(f"lattice_values should be nr_levels x capacity x 2, got {tuple(lv.shape)}")
+        if lv.dim() != 3 or tuple(lv.shape) != (fp.m_nr_levels, fp.m_capacity, self._feat):
+            raise RuntimeError(f"lattice_values should be nr_levels x capacity x {self._feat}, got {tuple(lv.shape)}")
         if not lv.is_contiguous():
             raise RuntimeError("We assume that the lattice_values_monolithic are contiguous because in the cuda "
                                "code we make a load of 2 float values at a time")

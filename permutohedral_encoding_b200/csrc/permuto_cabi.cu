@@ -27,7 +27,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-int extra_levels(int pos_dim, int concat) { return concat ? (pos_dim + 1) / 2 : 0; }
+int extra_levels(int pos_dim, int nr_feat, int concat) { return concat ? (pos_dim + nr_feat - 1) / nr_feat : 0; }
 
 // Checks shared by every entry point; the messages mirror the reference's CHECKs
 // (src/Encoding.cu:37-45, :63-66) and factory errors (Encoding.cuh:142,155).
@@ -35,9 +35,8 @@ int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::
     if (!cfg || !in) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "cfg and in must not be NULL");
     if (cfg->pos_dim < 2 || cfg->pos_dim > 7)
         return fail(PERMUTO_ERR_UNSUPPORTED, "Encoding: pos_dim must be 2,3,4,5,6 or 7 (got %d)", cfg->pos_dim);
-    if (cfg->nr_feat_per_level != 2)
-        return fail(PERMUTO_ERR_UNSUPPORTED,
-                    "Encoding: nr_feat_per_level must be 2 since other values are not yet implemented (got %d)",
+    if (cfg->nr_feat_per_level != 2 && cfg->nr_feat_per_level != 4 && cfg->nr_feat_per_level != 8)
+        return fail(PERMUTO_ERR_UNSUPPORTED, "Encoding: nr_feat_per_level must be 2, 4 or 8 (got %d)",
                     cfg->nr_feat_per_level);
     if (cfg->nr_levels < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "nr_levels must be >= 1");
     if (cfg->capacity < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "capacity must be >= 1");
@@ -47,9 +46,11 @@ int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::
     if (!in->positions || !in->lattice_values || !in->scale_factor || !in->random_shift || !in->anneal_window)
         return fail(PERMUTO_ERR_INVALID_ARGUMENT, "positions, lattice_values, scale_factor, random_shift and "
                                                   "anneal_window must not be NULL");
-    if (!aligned(in->lattice_values, 8))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_values must be 8-byte aligned (two features are moved at once)");
-    const int extra = extra_levels(cfg->pos_dim, cfg->concat_points);
+    const int F = cfg->nr_feat_per_level;
+    if (!aligned(in->lattice_values, 4 * (size_t)F))
+        return fail(PERMUTO_ERR_INVALID_ARGUMENT,
+                    "lattice_values must be %d-byte aligned (all features of a slot are moved at once)", 4 * F);
+    const int extra = extra_levels(cfg->pos_dim, F, cfg->concat_points);
     p.positions = in->positions;
     p.pos_stride_n = in->pos_stride_n;
     p.pos_stride_d = in->pos_stride_d;
@@ -61,7 +62,8 @@ int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::
     p.nr_levels = cfg->nr_levels;
     p.capacity = (uint32_t)cfg->capacity;
     p.cap_is_pow2 = (cfg->capacity & (cfg->capacity - 1)) == 0;
-    p.width = 2 * (cfg->nr_levels + extra);
+    p.nr_feat = F;
+    p.width = F * (cfg->nr_levels + extra);
     p.level_begin = 0;
     p.level_end = cfg->nr_levels;
     p.extra_levels = extra;
@@ -72,13 +74,16 @@ int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::
 }
 
 // feature rows can be moved 32 bytes at a time when every row segment starts on a 32-byte
-// boundary: base aligned, row pitch a multiple of 32 bytes, first level a multiple of 4
+// boundary: base aligned, row pitch a multiple of 32 bytes, first level on an 8-float boundary
 bool rows_vec8(const permuto::Problem& p, const void* a, const void* b) {
-    if ((p.width * 4) % 32 != 0 || p.level_begin % 4 != 0) return false;
+    if ((p.width * 4) % 32 != 0 || (p.level_begin * p.nr_feat) % 8 != 0) return false;
     if (a && !aligned(a, 32)) return false;
     if (b && !aligned(b, 32)) return false;
     return true;
 }
+
+// alignment of per-level accesses to rows and table entries: 8 bytes for F = 2, 16 for F = 4 and 8
+size_t row_align(const permuto::Problem& p) { return p.nr_feat == 2 ? 8 : 16; }
 
 #define PERMUTO_DISPATCH(fn, args, st)                                  \
     switch (cfg->pos_dim) {                                             \
@@ -98,7 +103,10 @@ int permuto_abi_version(void) { return PERMUTO_ABI_VERSION; }
 
 const char* permuto_last_error(void) { return g_error; }
 
-int permuto_extra_levels(int32_t pos_dim, int32_t concat_points) { return extra_levels(pos_dim, concat_points); }
+int permuto_extra_levels(int32_t pos_dim, int32_t nr_feat_per_level, int32_t concat_points) {
+    if (nr_feat_per_level < 1) return 0;
+    return extra_levels(pos_dim, nr_feat_per_level, concat_points);
+}
 
 int permuto_scale_factor(const double* sigmas, int32_t nr_levels, int32_t pos_dim, float* out_host) {
     if (!sigmas || !out_host) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "sigmas and out_host must not be NULL");
@@ -123,7 +131,7 @@ int permuto_forward(const permuto_config* cfg, const permuto_inputs* in, float* 
     permuto::ForwardArgs a;
     if (int rc = build_problem(cfg, in, a.p)) return rc;
     if (!features) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "features must not be NULL");
-    if (!aligned(features, 8)) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "features must be 8-byte aligned");
+    if (!aligned(features, row_align(a.p))) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "features must be %d-byte aligned", (int)row_align(a.p));
     a.features = features;
     a.p.rows_vec8_ok = rows_vec8(a.p, features, nullptr);
     cudaError_t err;
@@ -139,9 +147,10 @@ int permuto_backward(const permuto_config* cfg, const permuto_inputs* in, const 
     permuto::BackwardArgs a;
     if (int rc = build_problem(cfg, in, a.p)) return rc;
     if (!grad_features) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must not be NULL");
-    if (!aligned(grad_features, 8)) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be 8-byte aligned");
-    if (lattice_grad && !aligned(lattice_grad, 8))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be 8-byte aligned");
+    if (!aligned(grad_features, row_align(a.p)))
+        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be %d-byte aligned", (int)row_align(a.p));
+    if (lattice_grad && !aligned(lattice_grad, row_align(a.p)))
+        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be %d-byte aligned", (int)row_align(a.p));
     if (level_begin < 0 || level_end > cfg->nr_levels || level_begin > level_end)
         return fail(PERMUTO_ERR_INVALID_ARGUMENT, "level range [%d, %d) outside [0, %d)", level_begin, level_end,
                     cfg->nr_levels);
@@ -156,8 +165,8 @@ int permuto_backward(const permuto_config* cfg, const permuto_inputs* in, const 
     if (flags & PERMUTO_ZERO_OUTPUTS) {
         cudaError_t e = cudaSuccess;
         if (lattice_grad && level_end > level_begin)
-            e = cudaMemsetAsync(lattice_grad + (size_t)level_begin * a.p.capacity * 2u, 0,
-                                (size_t)(level_end - level_begin) * a.p.capacity * 2u * sizeof(float), st);
+            e = cudaMemsetAsync(lattice_grad + (size_t)level_begin * a.p.capacity * a.p.nr_feat, 0,
+                                (size_t)(level_end - level_begin) * a.p.capacity * a.p.nr_feat * sizeof(float), st);
         if (e == cudaSuccess && positions_grad && !(flags & PERMUTO_KEEP_POSITIONS_GRAD))
             e = cudaMemsetAsync(positions_grad, 0, (size_t)a.p.n_points * cfg->pos_dim * sizeof(float), st);
         if (e != cudaSuccess) return cuda_fail(e, "permuto_backward clearing outputs");
@@ -177,12 +186,12 @@ int permuto_double_backward(const permuto_config* cfg, const permuto_inputs* in,
     if (!double_positions_grad) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "double_positions_grad must not be NULL");
     if (lattice_grad && !grad_features)
         return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features is needed for the lattice gradient");
-    if (grad_features && !aligned(grad_features, 8))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be 8-byte aligned");
-    if (lattice_grad && !aligned(lattice_grad, 8))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be 8-byte aligned");
-    if (grad_grad_features && !aligned(grad_grad_features, 8))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_grad_features must be 8-byte aligned");
+    if (grad_features && !aligned(grad_features, row_align(a.p)))
+        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be %d-byte aligned", (int)row_align(a.p));
+    if (lattice_grad && !aligned(lattice_grad, row_align(a.p)))
+        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be %d-byte aligned", (int)row_align(a.p));
+    if (grad_grad_features && !aligned(grad_grad_features, row_align(a.p)))
+        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_grad_features must be %d-byte aligned", (int)row_align(a.p));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     a.double_positions_grad = double_positions_grad;
     a.grad_features = grad_features;
@@ -191,7 +200,7 @@ int permuto_double_backward(const permuto_config* cfg, const permuto_inputs* in,
     a.aggregate = (flags & PERMUTO_NO_AGGREGATE) ? 0 : 1;
     a.p.rows_vec8_ok = rows_vec8(a.p, grad_features, grad_grad_features);
     if ((flags & PERMUTO_ZERO_OUTPUTS) && lattice_grad) {
-        cudaError_t e = cudaMemsetAsync(lattice_grad, 0, (size_t)a.p.nr_levels * a.p.capacity * 2u * sizeof(float), st);
+        cudaError_t e = cudaMemsetAsync(lattice_grad, 0, (size_t)a.p.nr_levels * a.p.capacity * a.p.nr_feat * sizeof(float), st);
         if (e != cudaSuccess) return cuda_fail(e, "permuto_double_backward clearing outputs");
     }
     if (!lattice_grad && !grad_grad_features) return PERMUTO_OK;

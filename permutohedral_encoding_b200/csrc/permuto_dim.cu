@@ -1,13 +1,15 @@
 // Lattice kernels for one pos_dim (compile with -DPERMUTO_DIM=2..7), sm_100a.
 //
-// Work decomposition shared by all kernels: one thread owns one point and LPT consecutive
-// levels.  blockIdx.x walks point tiles, blockIdx.y walks level groups, and blocks are
-// dispatched x-fastest, so the whole grid sweeps the points once per level group: the
-// slices of the value table (and of its gradient) that are live at any time are the LPT
-// slices of one group, which stay L2-resident.  With LPT = 4 and two features per level a
-// thread produces / consumes 8 consecutive floats of a feature row = one 32-byte sector,
-// moved with a single 256-bit access (ld/st.global.v8.f32, new on sm_100), directly in the
-// final [N, 2L] layout -- no transposed intermediate.
+// Work decomposition shared by all kernels: one thread owns one point and walks levels in steps
+// of LPS levels.  blockIdx.x walks point tiles, blockIdx.y walks passes of `levels_per_pass`
+// levels, and blocks are dispatched x-fastest, so the whole grid sweeps the points once per
+// pass: the slices of the value table (and of its gradient) that are live at any time are those
+// of one pass, which stay L2-resident.  A step covers LPS = 8 / F levels of F features each,
+// i.e. 8 consecutive floats of a feature row = one 32-byte sector, moved with a single 256-bit
+// access (ld/st.global.v8.f32, new on sm_100), directly in the final [N, F*L] layout -- no
+// transposed intermediate.  F = 2 is the reference's only supported width; F = 4 and 8 (which
+// the reference lists as not yet implemented, Encoding.cuh:140-143) make every table access a
+// 16- or 32-byte one, i.e. half or all of the sector the memory system moves anyway.
 //
 // What each kernel replaces in the reference (paths relative to its root):
 //   forward_kernel          kernels/permutohedral_encoding/EncodingGPU.cuh:68-256
@@ -37,6 +39,12 @@ constexpr int D = PERMUTO_DIM;
 #define PERMUTO_MIN_BLOCKS_GATHER_ONLY (PERMUTO_DIM <= 4 ? 5 : 4)  // 5 spills and loses from pos_dim 5 up
 #endif
 constexpr int kThreads = PERMUTO_THREADS;
+// wider table entries keep more addends live per vertex: leave them more registers
+constexpr int min_blocks(int feats, bool gather_only) {
+    return feats == 8 ? 2
+                      : (feats == 4 || D >= 6) ? 3
+                                               : (gather_only ? PERMUTO_MIN_BLOCKS_GATHER_ONLY : PERMUTO_MIN_BLOCKS);
+}
 constexpr unsigned kFullMask = 0xffffffffu;
 
 __device__ __forceinline__ void load_pos(const Problem& p, int64_t n, float (&pos)[D]) {
@@ -56,7 +64,36 @@ __device__ __forceinline__ void to_slots(const Problem& p, const Simplex<D>& s, 
     }
 }
 
-// 8 consecutive floats of a feature row, 32-byte aligned
+// ---- F consecutive floats (one table entry, or one level of a feature row) ------------------
+template <int F>
+__device__ __forceinline__ void load_feats(const float* __restrict__ src, float (&v)[F]) {
+    if (F == 2) {
+        const float2 t = __ldg(reinterpret_cast<const float2*>(src));
+        v[0] = t.x;
+        v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int q = 0; q < F / 4; ++q) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(src) + q);
+            v[4 * q + 0] = t.x;
+            v[4 * q + 1] = t.y;
+            v[4 * q + 2] = t.z;
+            v[4 * q + 3] = t.w;
+        }
+    }
+}
+template <int F>
+__device__ __forceinline__ void store_feats(float* dst, const float (&v)[F]) {
+    if (F == 2) {
+        *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+    } else {
+#pragma unroll
+        for (int q = 0; q < F / 4; ++q)
+            reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+}
+
+// 8 consecutive floats of a feature row (or one 8-feature table entry), 32-byte aligned
 __device__ __forceinline__ void load8(const float* src, float (&v)[8]) {
     asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
@@ -68,48 +105,79 @@ __device__ __forceinline__ void store8(float* dst, const float (&v)[8]) {
                  : "memory");
 }
 
-// Row segment [2*l0, 2*(l0+LPT)) of point n: vector path when the whole group is inside the
-// level range and rows are 32-byte aligned, else per-level float2 accesses.
-template <int LPT>
-__device__ __forceinline__ void load_row_segment(const Problem& p, const float* rows, int64_t n, int l0,
-                                                 float (&v)[2 * LPT]) {
-    const float* src = rows + n * p.width + 2 * l0;
-    if (LPT == 4 && p.rows_vec8_ok && l0 + LPT <= p.level_end) {
-        float t[8];
-        load8(src, t);
-#pragma unroll
-        for (int i = 0; i < 2 * LPT; ++i) v[i] = t[i % 8];
+// aligned gather of one table entry (all F features) through the read-only path
+template <int F>
+__device__ __forceinline__ void gather(const float* __restrict__ level_base, uint32_t slot, float (&v)[F]) {
+    const float* src = level_base + (size_t)slot * F;
+    if (F == 8) {
+        asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+                     : "l"(src));
+    } else {
+        load_feats<F>(src, v);
+    }
+}
+
+// vector reduction of one table-gradient entry: 8 bytes (F = 2) or 16 bytes (F = 4) per L2
+// atomic -- both run at the same operation rate -- and two 16-byte ones for F = 8
+template <int F>
+__device__ __forceinline__ void red_add(float* level_base, uint32_t slot, const float (&x)[F]) {
+    float* p = level_base + (size_t)slot * F;
+    if (F == 2) {
+        asm volatile("red.relaxed.gpu.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(x[0]), "f"(x[1]) : "memory");
     } else {
 #pragma unroll
-        for (int k = 0; k < LPT; ++k) {
-            float2 g = make_float2(0.f, 0.f);
-            if (l0 + k < p.level_end) g = __ldg(reinterpret_cast<const float2*>(src) + k);
-            v[2 * k] = g.x;
-            v[2 * k + 1] = g.y;
+        for (int q = 0; q < F / 4; ++q)
+            asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p + 4 * q), "f"(x[4 * q]),
+                         "f"(x[4 * q + 1]), "f"(x[4 * q + 2]), "f"(x[4 * q + 3])
+                         : "memory");
+    }
+}
+
+// Row segment of point n starting at level l0: LPS levels of F floats.  One 32-byte vector access
+// when the segment is a whole, aligned 8-float group; else per-level accesses.
+template <int F, int LPS>
+__device__ __forceinline__ void load_row_segment(const Problem& p, const float* rows, int64_t n, int l0,
+                                                 float (&v)[F * LPS]) {
+    const float* src = rows + n * p.width + F * l0;
+    if (F * LPS == 8 && p.rows_vec8_ok && l0 + LPS <= p.level_end) {
+        load8(src, reinterpret_cast<float(&)[8]>(v));
+    } else {
+#pragma unroll
+        for (int k = 0; k < LPS; ++k) {
+            float t[F];
+#pragma unroll
+            for (int f = 0; f < F; ++f) t[f] = 0.f;
+            if (l0 + k < p.level_end) load_feats<F>(src + F * k, t);
+#pragma unroll
+            for (int f = 0; f < F; ++f) v[F * k + f] = t[f];
         }
     }
 }
-template <int LPT>
+template <int F, int LPS>
 __device__ __forceinline__ void store_row_segment(const Problem& p, float* rows, int64_t n, int l0,
-                                                  const float (&v)[2 * LPT]) {
-    float* dst = rows + n * p.width + 2 * l0;
-    if (LPT == 4 && p.rows_vec8_ok && l0 + LPT <= p.level_end) {
-        float t[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = v[i % (2 * LPT)];
-        store8(dst, t);
+                                                  const float (&v)[F * LPS]) {
+    float* dst = rows + n * p.width + F * l0;
+    if (F * LPS == 8 && p.rows_vec8_ok && l0 + LPS <= p.level_end) {
+        store8(dst, reinterpret_cast<const float(&)[8]>(v));
     } else {
 #pragma unroll
-        for (int k = 0; k < LPT; ++k)
-            if (l0 + k < p.level_end) reinterpret_cast<float2*>(dst)[k] = make_float2(v[2 * k], v[2 * k + 1]);
+        for (int k = 0; k < LPS; ++k) {
+            if (l0 + k < p.level_end) {
+                float t[F];
+#pragma unroll
+                for (int f = 0; f < F; ++f) t[f] = v[F * k + f];
+                store_feats<F>(dst + F * k, t);
+            }
+        }
     }
 }
 
 // ------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------
-template <int LPT>
-__global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) forward_kernel(const ForwardArgs a) {
+template <int F, int LPS>
+__global__ void __launch_bounds__(kThreads, min_blocks(F, false)) forward_kernel(const ForwardArgs a) {
     const Problem& p = a.p;
     const int64_t n = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (n >= p.n_points) return;
@@ -120,41 +188,43 @@ __global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) forward_kernel(c
     load_pos(p, n, pos);
 
 #pragma unroll 1
-    for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
-    float out[2 * LPT];
+    for (int l0 = pass_begin; l0 < pass_end; l0 += LPS) {
+        float out[F * LPS];
 #pragma unroll
-    for (int k = 0; k < LPT; ++k) {
-        const int l = l0 + k;
-        float ax = 0.f, ay = 0.f;
-        if (l < pass_end) {  // uniform over the block
-            const float w_lvl = __ldg(p.anneal + l);
-            if (w_lvl != 0.0f) {  // a closed coarse-to-fine window contributes exact zeros
-                Simplex<D> s;
-                locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-                uint32_t slot[D + 1];
-                to_slots(p, s, slot);
-                const float* base = p.table + (size_t)l * p.capacity * 2u;
-                float2 v[D + 1];
+        for (int k = 0; k < LPS; ++k) {
+            const int l = l0 + k;
+            float acc[F];
 #pragma unroll
-                for (int r = 0; r <= D; ++r) v[r] = gather2(base, slot[r]);
+            for (int f = 0; f < F; ++f) acc[f] = 0.f;
+            if (l < pass_end) {  // uniform over the block
+                const float w_lvl = __ldg(p.anneal + l);
+                if (w_lvl != 0.0f) {  // a closed coarse-to-fine window contributes exact zeros
+                    Simplex<D> s;
+                    locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+                    uint32_t slot[D + 1];
+                    to_slots(p, s, slot);
+                    const float* base = p.table + (size_t)l * p.capacity * F;
+                    float v[D + 1][F];
 #pragma unroll
-                for (int r = 0; r <= D; ++r) {
-                    const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:234
-                    ax = fmaf(v[r].x, w, ax);
-                    ay = fmaf(v[r].y, w, ay);
+                    for (int r = 0; r <= D; ++r) gather<F>(base, slot[r], v[r]);
+#pragma unroll
+                    for (int r = 0; r <= D; ++r) {
+                        const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:234
+#pragma unroll
+                        for (int f = 0; f < F; ++f) acc[f] = fmaf(v[r][f], w, acc[f]);
+                    }
                 }
             }
+#pragma unroll
+            for (int f = 0; f < F; ++f) out[F * k + f] = acc[f];
         }
-        out[2 * k] = ax;
-        out[2 * k + 1] = ay;
-    }
-    store_row_segment<LPT>(p, a.features, n, l0, out);
+        store_row_segment<F, LPS>(p, a.features, n, l0, out);
     }
 
     // raw points appended after the lattice levels (EncodingGPU.cuh:105-121)
     if (p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {
-        float* dst = a.features + n * p.width + 2 * p.nr_levels;
-        for (int c = 0; c < 2 * p.extra_levels; ++c) {
+        float* dst = a.features + n * p.width + F * p.nr_levels;
+        for (int c = 0; c < F * p.extra_levels; ++c) {
             float v = 0.f;
 #pragma unroll
             for (int i = 0; i < D; ++i) v = (c == i) ? pos[i] * p.points_scaling : v;
@@ -172,24 +242,26 @@ __global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) forward_kernel(c
 // lanes (log2 of the largest group rounds) leaves the group total in its lowest lane, and only
 // that lane issues the vector reduction.  The summation order is fixed by the lane order, so a
 // warp's contribution is deterministic.
-__device__ __forceinline__ void merge_and_red(float* level_base, uint32_t slot, float x, float y, bool active,
+template <int F>
+__device__ __forceinline__ void merge_and_red(float* level_base, uint32_t slot, float (&x)[F], bool active,
                                               unsigned lane, unsigned group) {
     const int largest = __reduce_max_sync(kFullMask, __popc(group));
     const unsigned above = group & (0xfffffffeu << lane);
     int next = above ? (__ffs(above) - 1) : -1;
     for (int span = 1; span < largest; span <<= 1) {  // warp-uniform trip count
         const int src = next >= 0 ? next : (int)lane;
-        const float x2 = __shfl_sync(kFullMask, x, src);
-        const float y2 = __shfl_sync(kFullMask, y, src);
+        float x2[F];
+#pragma unroll
+        for (int f = 0; f < F; ++f) x2[f] = __shfl_sync(kFullMask, x[f], src);
         const int n2 = __shfl_sync(kFullMask, next, src);
         if (next >= 0) {
-            x += x2;
-            y += y2;
+#pragma unroll
+            for (int f = 0; f < F; ++f) x[f] += x2[f];
             next = n2;
         }
     }
     const bool leader = (group & ((1u << lane) - 1u)) == 0u;
-    if (leader && active) red_add2(level_base, slot, x, y);
+    if (leader && active) red_add<F>(level_base, slot, x);
 }
 
 // Merging pays only while a warp's 32 points share slots: per warp and vertex the number of
@@ -203,19 +275,20 @@ __device__ __forceinline__ void merge_and_red(float* level_base, uint32_t slot, 
 #endif
 constexpr int kMergeBelow = PERMUTO_MERGE_BELOW;
 
-__device__ __forceinline__ void scatter_level(float* level_base, const uint32_t (&slot)[D + 1], const float (&ax)[D + 1],
-                                              const float (&ay)[D + 1], bool active, unsigned lane, bool& probe) {
+template <int F>
+__device__ __forceinline__ void scatter_level(float* level_base, const uint32_t (&slot)[D + 1], float (&add)[D + 1][F],
+                                              bool active, unsigned lane, bool& probe) {
     if (probe) {
         const uint32_t idle = 0xffffffffu - lane;  // idle lanes match nobody
         const unsigned group0 = __match_any_sync(kFullMask, active ? slot[0] : idle);
         const bool leader0 = (group0 & ((1u << lane) - 1u)) == 0u;
         const int distinct = __popc(__ballot_sync(kFullMask, leader0));
         if (distinct <= kMergeBelow) {
-            merge_and_red(level_base, slot[0], ax[0], ay[0], active, lane, group0);
+            merge_and_red<F>(level_base, slot[0], add[0], active, lane, group0);
 #pragma unroll
             for (int r = 1; r <= D; ++r) {
                 const unsigned group = __match_any_sync(kFullMask, active ? slot[r] : idle);
-                merge_and_red(level_base, slot[r], ax[r], ay[r], active, lane, group);
+                merge_and_red<F>(level_base, slot[r], add[r], active, lane, group);
             }
             return;
         }
@@ -223,15 +296,16 @@ __device__ __forceinline__ void scatter_level(float* level_base, const uint32_t 
     }
     if (active) {
 #pragma unroll
-        for (int r = 0; r <= D; ++r) red_add2(level_base, slot[r], ax[r], ay[r]);
+        for (int r = 0; r <= D; ++r) red_add<F>(level_base, slot[r], add[r]);
     }
 }
 
 // ------------------------------------------------------------------------------------------
 // first-order backward: table gradient (scatter) and/or position gradient (gather)
 // ------------------------------------------------------------------------------------------
-template <int LPT, bool TABLE, bool POS>
-__global__ void __launch_bounds__(kThreads, (TABLE ? PERMUTO_MIN_BLOCKS : PERMUTO_MIN_BLOCKS_GATHER_ONLY)) backward_kernel(const BackwardArgs a) {
+template <int F, int LPS, bool TABLE, bool POS>
+__global__ void __launch_bounds__(kThreads, min_blocks(F, !TABLE))
+backward_kernel(const BackwardArgs a) {
     const Problem& p = a.p;
     const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     const bool active = n_raw < p.n_points;
@@ -249,83 +323,90 @@ __global__ void __launch_bounds__(kThreads, (TABLE ? PERMUTO_MIN_BLOCKS : PERMUT
     for (int i = 0; i < D; ++i) dpos[i] = 0.f;
     bool probe = a.aggregate != 0;
 
-    // the next group's 32 bytes of the gradient row are requested before this group is worked on
-    float g_next[2 * LPT];
-    load_row_segment<LPT>(p, a.grad_features, n, pass_begin, g_next);
+    // the next step's 32 bytes of the gradient row are requested before this step is worked on
+    float g_next[F * LPS];
+    load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin, g_next);
 #pragma unroll 1
-    for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
-    float g[2 * LPT];
+    for (int l0 = pass_begin; l0 < pass_end; l0 += LPS) {
+        float g[F * LPS];
 #pragma unroll
-    for (int i = 0; i < 2 * LPT; ++i) g[i] = g_next[i];
-    if (l0 + LPT < pass_end) load_row_segment<LPT>(p, a.grad_features, n, l0 + LPT, g_next);
+        for (int i = 0; i < F * LPS; ++i) g[i] = g_next[i];
+        if (l0 + LPS < pass_end) load_row_segment<F, LPS>(p, a.grad_features, n, l0 + LPS, g_next);
 #pragma unroll
-    for (int k = 0; k < LPT; ++k) {
-        const int l = l0 + k;
-        if (l >= pass_end) continue;  // uniform
-        const float w_lvl = __ldg(p.anneal + l);
-        if (w_lvl == 0.0f) continue;  // every addend of this level is an exact zero
-        Simplex<D> s;
-        locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-        uint32_t slot[D + 1];
-        to_slots(p, s, slot);
-        const float gx = g[2 * k], gy = g[2 * k + 1];
+        for (int k = 0; k < LPS; ++k) {
+            const int l = l0 + k;
+            if (l >= pass_end) continue;  // uniform
+            const float w_lvl = __ldg(p.anneal + l);
+            if (w_lvl == 0.0f) continue;  // every addend of this level is an exact zero
+            Simplex<D> s;
+            locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+            uint32_t slot[D + 1];
+            to_slots(p, s, slot);
 
-        if (POS) {
-            // EncodingGPU.cuh:671-749
-            const float* base = p.table + (size_t)l * p.capacity * 2u;
-            float dBs[D + 2];
-            const float gxs = gx * w_lvl * kInv, gys = gy * w_lvl * kInv;  // level weight and 1/(d+1) folded in
+            if (POS) {
+                // EncodingGPU.cuh:671-749
+                const float* base = p.table + (size_t)l * p.capacity * F;
+                float gs[F];  // upstream gradient with the level weight and 1/(d+1) folded in
 #pragma unroll
-            for (int r = 0; r <= D; ++r) {
-                const float2 v = gather2(base, slot[r]);
-                dBs[r] = fmaf(v.y, gys, v.x * gxs);
+                for (int f = 0; f < F; ++f) gs[f] = g[F * k + f] * w_lvl * kInv;
+                float dBs[D + 2];
+#pragma unroll
+                for (int r = 0; r <= D; ++r) {
+                    float v[F];
+                    gather<F>(base, slot[r], v);
+                    float t = v[0] * gs[0];
+#pragma unroll
+                    for (int f = 1; f < F; ++f) t = fmaf(v[f], gs[f], t);
+                    dBs[r] = t;
+                }
+                dBs[D + 1] = dBs[0];
+                float T[D + 1];  // dE of the coordinate whose rank is k
+#pragma unroll
+                for (int kk = 0; kk <= D; ++kk) T[kk] = dBs[D - kk] - dBs[D + 1 - kk];
+                float dE[D + 1];
+#pragma unroll
+                for (int i = 0; i <= D; ++i) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int kk = 0; kk <= D; ++kk) v = (s.rank[i] == kk) ? T[kk] : v;
+                    dE[i] = v;
+                }
+                float run = 0.f;
+#pragma unroll
+                for (int i = 0; i < D; ++i) {
+                    run += dE[i];
+                    const float sc = __ldg(p.scale + l * D + i);
+                    dpos[i] += sc * (run - (float)(i + 1) * dE[i + 1]);
+                }
             }
-            dBs[D + 1] = dBs[0];
-            float T[D + 1];  // dE of the coordinate whose rank is k
+
+            if (TABLE) {
+                float* gbase = a.lattice_grad + (size_t)l * p.capacity * F;
+                float gw[F];  // EncodingGPU.cuh:405-410
 #pragma unroll
-            for (int kk = 0; kk <= D; ++kk) T[kk] = dBs[D - kk] - dBs[D + 1 - kk];
-            float dE[D + 1];
+                for (int f = 0; f < F; ++f) gw[f] = g[F * k + f] * w_lvl;
+                float add[D + 1][F];
 #pragma unroll
-            for (int i = 0; i <= D; ++i) {
-                float v = 0.f;
+                for (int r = 0; r <= D; ++r) {
 #pragma unroll
-                for (int kk = 0; kk <= D; ++kk) v = (s.rank[i] == kk) ? T[kk] : v;
-                dE[i] = v;
-            }
-            float run = 0.f;
-#pragma unroll
-            for (int i = 0; i < D; ++i) {
-                run += dE[i];
-                const float sc = __ldg(p.scale + l * D + i);
-                dpos[i] += sc * (run - (float)(i + 1) * dE[i + 1]);
+                    for (int f = 0; f < F; ++f) add[r][f] = s.bary[r] * gw[f];
+                }
+                scatter_level<F>(gbase, slot, add, active, lane, probe);
             }
         }
-
-        if (TABLE) {
-            float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
-            float ax[D + 1], ay[D + 1];
-            const float gxw = gx * w_lvl, gyw = gy * w_lvl;  // EncodingGPU.cuh:405-410
-#pragma unroll
-            for (int r = 0; r <= D; ++r) {
-                ax[r] = s.bary[r] * gxw;
-                ay[r] = s.bary[r] * gyw;
-            }
-            scatter_level(gbase, slot, ax, ay, active, lane, probe);
-        }
-    }
     }
     if (POS && active) {
         float* dst = a.positions_grad + n * D;
 #pragma unroll
-        for (int i = 0; i < D; ++i) red_add1(dst + i, dpos[i]);  // accumulates across level groups
+        for (int i = 0; i < D; ++i) red_add1(dst + i, dpos[i]);  // accumulates across passes
     }
 }
 
 // ------------------------------------------------------------------------------------------
 // double backward of the position gradient
 // ------------------------------------------------------------------------------------------
-template <int LPT, bool TABLE, bool GGF>
-__global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) double_backward_kernel(const DoubleBackwardArgs a) {
+template <int F, int LPS, bool TABLE, bool GGF>
+__global__ void __launch_bounds__(kThreads, min_blocks(F, false)) double_backward_kernel(const DoubleBackwardArgs a) {
     const Problem& p = a.p;
     const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     const bool active = n_raw < p.n_points;
@@ -341,88 +422,88 @@ __global__ void __launch_bounds__(kThreads, PERMUTO_MIN_BLOCKS) double_backward_
     for (int i = 0; i < D; ++i) dpg[i] = __ldg(a.double_positions_grad + n * D + i);
     bool probe = a.aggregate != 0;  // as in backward_kernel
 
-    float g_next[2 * LPT];  // as in backward_kernel: the next group's gradient segment is requested early
-    if (TABLE) load_row_segment<LPT>(p, a.grad_features, n, pass_begin, g_next);
+    float g_next[F * LPS];  // as in backward_kernel: the next step's gradient segment is requested early
+    if (TABLE) load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin, g_next);
 #pragma unroll 1
-    for (int l0 = pass_begin; l0 < pass_end; l0 += LPT) {
-    float g[2 * LPT];
-    if (TABLE) {
+    for (int l0 = pass_begin; l0 < pass_end; l0 += LPS) {
+        float g[F * LPS];
+        if (TABLE) {
 #pragma unroll
-        for (int i = 0; i < 2 * LPT; ++i) g[i] = g_next[i];
-        if (l0 + LPT < pass_end) load_row_segment<LPT>(p, a.grad_features, n, l0 + LPT, g_next);
-    }
-    float out[2 * LPT];
+            for (int i = 0; i < F * LPS; ++i) g[i] = g_next[i];
+            if (l0 + LPS < pass_end) load_row_segment<F, LPS>(p, a.grad_features, n, l0 + LPS, g_next);
+        }
+        float out[F * LPS];
 #pragma unroll
-    for (int k = 0; k < LPT; ++k) {
-        const int l = l0 + k;
-        float ox = 0.f, oy = 0.f;
-        if (l < pass_end) {
-            const float w_lvl = __ldg(p.anneal + l);
-            if (w_lvl != 0.0f) {
-                Simplex<D> s;
-                locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-                uint32_t slot[D + 1];
-                to_slots(p, s, slot);
+        for (int k = 0; k < LPS; ++k) {
+            const int l = l0 + k;
+            float o[F];
+#pragma unroll
+            for (int f = 0; f < F; ++f) o[f] = 0.f;
+            if (l < pass_end) {
+                const float w_lvl = __ldg(p.anneal + l);
+                if (w_lvl != 0.0f) {
+                    Simplex<D> s;
+                    locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+                    uint32_t slot[D + 1];
+                    to_slots(p, s, slot);
 
-                // d loss / d elevated (EncodingGPU.cuh:1187-1199)
-                float gs[D], dE[D + 1];
+                    // d loss / d elevated (EncodingGPU.cuh:1187-1199)
+                    float gsd[D], dE[D + 1];
 #pragma unroll
-                for (int i = 0; i < D; ++i) gs[i] = dpg[i] * __ldg(p.scale + l * D + i);
+                    for (int i = 0; i < D; ++i) gsd[i] = dpg[i] * __ldg(p.scale + l * D + i);
 #pragma unroll
-                for (int j = 0; j <= D; ++j) dE[j] = 0.f;
+                    for (int j = 0; j <= D; ++j) dE[j] = 0.f;
 #pragma unroll
-                for (int i = 0; i < D; ++i) {
+                    for (int i = 0; i < D; ++i) {
 #pragma unroll
-                    for (int j = 0; j <= i; ++j) dE[j] += gs[i];
-                }
+                        for (int j = 0; j <= i; ++j) dE[j] += gsd[i];
+                    }
 #pragma unroll
-                for (int i = 0; i < D; ++i) dE[i + 1] -= gs[i] * (float)(i + 1);
-                // d loss / d barycentric (EncodingGPU.cuh:1213-1218), via the rank-sorted vector
-                float sdE[D + 1];
+                    for (int i = 0; i < D; ++i) dE[i + 1] -= gsd[i] * (float)(i + 1);
+                    // d loss / d barycentric (EncodingGPU.cuh:1213-1218), via the rank-sorted vector
+                    float sdE[D + 1];
 #pragma unroll
-                for (int kk = 0; kk <= D; ++kk) {
-                    float v = 0.f;
+                    for (int kk = 0; kk <= D; ++kk) {
+                        float v = 0.f;
 #pragma unroll
-                    for (int i = 0; i <= D; ++i) v = (s.rank[i] == kk) ? dE[i] * kInv : v;
-                    sdE[kk] = v;
-                }
-                float dB[D + 1];
+                        for (int i = 0; i <= D; ++i) v = (s.rank[i] == kk) ? dE[i] * kInv : v;
+                        sdE[kk] = v;
+                    }
+                    float dBw[D + 1];  // dB * level weight
 #pragma unroll
-                for (int m = 1; m <= D; ++m) dB[m] = sdE[D - m] - sdE[D + 1 - m];
-                dB[0] = sdE[D] - sdE[0];
+                    for (int m = 1; m <= D; ++m) dBw[m] = (sdE[D - m] - sdE[D + 1 - m]) * w_lvl;
+                    dBw[0] = (sdE[D] - sdE[0]) * w_lvl;
 
-                if (GGF) {
-                    const float* base = p.table + (size_t)l * p.capacity * 2u;
+                    if (GGF) {
+                        const float* base = p.table + (size_t)l * p.capacity * F;
 #pragma unroll
-                    for (int r = 0; r <= D; ++r) {
-                        const float2 v = gather2(base, slot[r]);
-                        const float c = dB[r] * w_lvl;  // EncodingGPU.cuh:1484-1485
-                        ox = fmaf(c, v.x, ox);
-                        oy = fmaf(c, v.y, oy);
-                    }
-                }
-                if (TABLE) {
-                    float* gbase = a.lattice_grad + (size_t)l * p.capacity * 2u;
-                    const float gx = g[2 * k], gy = g[2 * k + 1];
-                    float ax[D + 1], ay[D + 1];
+                        for (int r = 0; r <= D; ++r) {
+                            float v[F];
+                            gather<F>(base, slot[r], v);  // EncodingGPU.cuh:1484-1485
 #pragma unroll
-                    for (int r = 0; r <= D; ++r) {
-                        const float c = dB[r] * w_lvl;  // EncodingGPU.cuh:1244-1245
-                        ax[r] = c * gx;
-                        ay[r] = c * gy;
+                            for (int f = 0; f < F; ++f) o[f] = fmaf(dBw[r], v[f], o[f]);
+                        }
                     }
-                    scatter_level(gbase, slot, ax, ay, active, lane, probe);
+                    if (TABLE) {
+                        float* gbase = a.lattice_grad + (size_t)l * p.capacity * F;
+                        float add[D + 1][F];
+#pragma unroll
+                        for (int r = 0; r <= D; ++r) {
+#pragma unroll
+                            for (int f = 0; f < F; ++f) add[r][f] = dBw[r] * g[F * k + f];  // EncodingGPU.cuh:1244-1245
+                        }
+                        scatter_level<F>(gbase, slot, add, active, lane, probe);
+                    }
                 }
             }
+#pragma unroll
+            for (int f = 0; f < F; ++f) out[F * k + f] = o[f];
         }
-        out[2 * k] = ox;
-        out[2 * k + 1] = oy;
-    }
-    if (GGF && active) store_row_segment<LPT>(p, a.grad_grad_features, n, l0, out);
+        if (GGF && active) store_row_segment<F, LPS>(p, a.grad_grad_features, n, l0, out);
     }
     if (GGF && active && p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {  // EncodingGPU.cuh:1290-1295
-        float* dst = a.grad_grad_features + n * p.width + 2 * p.nr_levels;
-        for (int c = 0; c < 2 * p.extra_levels; ++c) dst[c] = 0.f;
+        float* dst = a.grad_grad_features + n * p.width + F * p.nr_levels;
+        for (int c = 0; c < F * p.extra_levels; ++c) dst[c] = 0.f;
     }
 }
 
@@ -455,21 +536,22 @@ __global__ void __launch_bounds__(kThreads) debug_kernel(const DebugArgs a) {
     }
 }
 
-// Levels handled by one thread in one sweep over the points.  A multiple of 4 (one 32-byte row
-// segment per inner step).  More levels per pass means fewer sweeps -- each sweep re-reads the
-// positions and touches only its own 32-byte pieces of every 128-byte line of the feature rows,
-// which costs a 4x DRAM over-fetch on the gradient reads with one group per sweep -- but a larger
-// set of table slices is live in L2 at once: capacity * 8 bytes per level for the values and as
-// much again for their gradient.  Measured on B200 (pos_dim 3 and 4, capacities 2^18..2^20):
-// scatter-only kernels are fastest with every level in one sweep even when the gradient table
-// exceeds L2; gather kernels want about 96 MB live, gather+scatter kernels about 64 MB.
+// Levels handled by one thread in one sweep over the points.  A multiple of the levels per step
+// (one 32-byte row segment per step).  More levels per pass means fewer sweeps -- each sweep
+// re-reads the positions and touches only its own 32-byte pieces of every 128-byte line of the
+// feature rows, which costs a 4x DRAM over-fetch on the gradient reads with one step per sweep
+// -- but a larger set of table slices is live in L2 at once: capacity * 4F bytes per level for
+// the values and as much again for their gradient.  Measured on B200 (pos_dim 3 and 4,
+// capacities 2^18..2^20, F = 2): scatter-only kernels are fastest with every level in one sweep
+// even when the gradient table exceeds L2; gather kernels want about 96 MB live, gather+scatter
+// kernels about 64 MB.
 enum class Traffic { Gather, Scatter, Both };
 
-inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t) {
+inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t, int lps) {
     const int levels = p.level_end - p.level_begin;
     int lpp = requested;
     if (lpp <= 0) {
-        const double slice = 8.0 * p.capacity;
+        const double slice = 4.0 * p.nr_feat * p.capacity;
         const double mb = 1024.0 * 1024.0;
         if (t == Traffic::Scatter)
             lpp = levels;
@@ -478,9 +560,9 @@ inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t) {
         else
             lpp = (int)(64.0 * mb / (2.0 * slice));
     }
-    lpp = (lpp / 4) * 4;
-    if (lpp < 4) lpp = 4;
-    if (lpp > levels) lpp = ((levels + 3) / 4) * 4;
+    lpp = (lpp / lps) * lps;
+    if (lpp < lps) lpp = lps;
+    if (lpp > levels) lpp = ((levels + lps - 1) / lps) * lps;
     return lpp;
 }
 
@@ -490,19 +572,59 @@ inline dim3 grid_for(const Problem& p) {
     return dim3(gx, gy, 1);
 }
 
-// small problems get one level per thread so that the grid still covers the machine
+// small problems get one level per thread and pass so that the grid still covers the machine
 inline bool use_single_level(const Problem& p) {
-    const int64_t groups4 = (p.level_end - p.level_begin + 3) / 4;
-    const int64_t blocks4 = ((p.n_points + kThreads - 1) / kThreads) * groups4;
-    return blocks4 < 2 * 148;
+    const int lps = 8 / p.nr_feat;
+    const int64_t steps = (p.level_end - p.level_begin + lps - 1) / lps;
+    const int64_t blocks = ((p.n_points + kThreads - 1) / kThreads) * steps;
+    return lps > 1 && blocks < 2 * 148;
 }
 
 template <class Args>
 inline Args with_schedule(const Args& in, bool single, Traffic t) {
     Args a = in;
-    a.p.levels_per_pass = single ? 1 : pick_levels_per_pass(a.p, a.p.levels_per_pass, t);
+    a.p.levels_per_pass = single ? 1 : pick_levels_per_pass(a.p, a.p.levels_per_pass, t, 8 / a.p.nr_feat);
     return a;
 }
+
+template <int F, int LPS>
+cudaError_t launch_forward(const ForwardArgs& a, cudaStream_t st) {
+    forward_kernel<F, LPS><<<grid_for(a.p), kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+template <int F, int LPS>
+cudaError_t launch_backward(const BackwardArgs& a, cudaStream_t st) {
+    const dim3 g = grid_for(a.p);
+    if (a.lattice_grad && a.positions_grad)
+        backward_kernel<F, LPS, true, true><<<g, kThreads, 0, st>>>(a);
+    else if (a.lattice_grad)
+        backward_kernel<F, LPS, true, false><<<g, kThreads, 0, st>>>(a);
+    else if (a.positions_grad)
+        backward_kernel<F, LPS, false, true><<<g, kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+template <int F, int LPS>
+cudaError_t launch_double(const DoubleBackwardArgs& a, cudaStream_t st) {
+    const dim3 g = grid_for(a.p);
+    if (a.lattice_grad && a.grad_grad_features)
+        double_backward_kernel<F, LPS, true, true><<<g, kThreads, 0, st>>>(a);
+    else if (a.lattice_grad)
+        double_backward_kernel<F, LPS, true, false><<<g, kThreads, 0, st>>>(a);
+    else if (a.grad_grad_features)
+        double_backward_kernel<F, LPS, false, true><<<g, kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+// feature width and step size are compile-time: pick the instantiation
+#define PERMUTO_BY_WIDTH(fn, a, single, st)                                              \
+    switch ((a).p.nr_feat) {                                                             \
+        case 2: return (single) ? fn<2, 1>(a, st) : fn<2, 4>(a, st);                     \
+        case 4: return (single) ? fn<4, 1>(a, st) : fn<4, 2>(a, st);                     \
+        case 8: return fn<8, 1>(a, st);                                                  \
+        default: return cudaErrorInvalidValue;                                           \
+    }
 
 }  // namespace
 
@@ -512,48 +634,24 @@ inline Args with_schedule(const Args& in, bool single, Traffic t) {
 cudaError_t PERMUTO_CAT(launch_forward_dim, PERMUTO_DIM)(const ForwardArgs& a0, cudaStream_t st) {
     const bool single = use_single_level(a0.p);
     const ForwardArgs a = with_schedule(a0, single, Traffic::Gather);
-    if (single)
-        forward_kernel<1><<<grid_for(a.p), kThreads, 0, st>>>(a);
-    else
-        forward_kernel<4><<<grid_for(a.p), kThreads, 0, st>>>(a);
-    return cudaGetLastError();
+    PERMUTO_BY_WIDTH(launch_forward, a, single, st)
 }
 
-template <int LPT>
-static cudaError_t launch_backward_lpt(const BackwardArgs& a0, cudaStream_t st) {
-    const BackwardArgs a = with_schedule(
-        a0, LPT == 1, (a0.lattice_grad && a0.positions_grad) ? Traffic::Both : (a0.lattice_grad ? Traffic::Scatter : Traffic::Gather));
-    const dim3 g = grid_for(a.p);
-    if (a.lattice_grad && a.positions_grad)
-        backward_kernel<LPT, true, true><<<g, kThreads, 0, st>>>(a);
-    else if (a.lattice_grad)
-        backward_kernel<LPT, true, false><<<g, kThreads, 0, st>>>(a);
-    else if (a.positions_grad)
-        backward_kernel<LPT, false, true><<<g, kThreads, 0, st>>>(a);
-    return cudaGetLastError();
+cudaError_t PERMUTO_CAT(launch_backward_dim, PERMUTO_DIM)(const BackwardArgs& a0, cudaStream_t st) {
+    const bool single = use_single_level(a0.p);
+    const Traffic t = (a0.lattice_grad && a0.positions_grad) ? Traffic::Both
+                                                             : (a0.lattice_grad ? Traffic::Scatter : Traffic::Gather);
+    const BackwardArgs a = with_schedule(a0, single, t);
+    PERMUTO_BY_WIDTH(launch_backward, a, single, st)
 }
 
-cudaError_t PERMUTO_CAT(launch_backward_dim, PERMUTO_DIM)(const BackwardArgs& a, cudaStream_t st) {
-    return use_single_level(a.p) ? launch_backward_lpt<1>(a, st) : launch_backward_lpt<4>(a, st);
-}
-
-template <int LPT>
-static cudaError_t launch_double_lpt(const DoubleBackwardArgs& a0, cudaStream_t st) {
-    const DoubleBackwardArgs a = with_schedule(
-        a0, LPT == 1,
-        (a0.lattice_grad && a0.grad_grad_features) ? Traffic::Both : (a0.lattice_grad ? Traffic::Scatter : Traffic::Gather));
-    const dim3 g = grid_for(a.p);
-    if (a.lattice_grad && a.grad_grad_features)
-        double_backward_kernel<LPT, true, true><<<g, kThreads, 0, st>>>(a);
-    else if (a.lattice_grad)
-        double_backward_kernel<LPT, true, false><<<g, kThreads, 0, st>>>(a);
-    else if (a.grad_grad_features)
-        double_backward_kernel<LPT, false, true><<<g, kThreads, 0, st>>>(a);
-    return cudaGetLastError();
-}
-
-cudaError_t PERMUTO_CAT(launch_double_backward_dim, PERMUTO_DIM)(const DoubleBackwardArgs& a, cudaStream_t st) {
-    return use_single_level(a.p) ? launch_double_lpt<1>(a, st) : launch_double_lpt<4>(a, st);
+cudaError_t PERMUTO_CAT(launch_double_backward_dim, PERMUTO_DIM)(const DoubleBackwardArgs& a0, cudaStream_t st) {
+    const bool single = use_single_level(a0.p);
+    const Traffic t = (a0.lattice_grad && a0.grad_grad_features)
+                          ? Traffic::Both
+                          : (a0.lattice_grad ? Traffic::Scatter : Traffic::Gather);
+    const DoubleBackwardArgs a = with_schedule(a0, single, t);
+    PERMUTO_BY_WIDTH(launch_double, a, single, st)
 }
 
 cudaError_t PERMUTO_CAT(launch_debug_dim, PERMUTO_DIM)(const DebugArgs& a, cudaStream_t st) {

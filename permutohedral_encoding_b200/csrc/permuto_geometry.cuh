@@ -180,17 +180,6 @@ __device__ __forceinline__ void vertex_key(const Simplex<D>& s, int r, int (&key
     for (int i = 0; i < D; ++i) key[i] = s.rem0[i] + r - ((s.rank[i] > D - r) ? (D + 1) : 0);
 }
 
-// aligned 8-byte gather of one table entry (both features) through the read-only path
-__device__ __forceinline__ float2 gather2(const float* __restrict__ level_base, uint32_t slot) {
-    return __ldg(reinterpret_cast<const float2*>(level_base) + slot);
-}
-
-// one 8-byte vector reduction: both features of a table-gradient entry in a single L2 atomic
-__device__ __forceinline__ void red_add2(float* level_base, uint32_t slot, float x, float y) {
-    float* p = level_base + 2ull * slot;
-    asm volatile("red.relaxed.gpu.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(x), "f"(y) : "memory");
-}
-
 __device__ __forceinline__ void red_add1(float* p, float x) {
     asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(x) : "memory");
 }

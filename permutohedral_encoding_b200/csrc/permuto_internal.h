@@ -11,7 +11,7 @@ struct Problem {
     const float* positions;
     int64_t pos_stride_n;
     int64_t pos_stride_d;
-    const float* table;   // [L, C, 2]
+    const float* table;   // [L, C, F]
     const float* scale;   // [L, D]
     const float* shift;   // [L, D]
     const float* anneal;  // [L]
@@ -19,7 +19,8 @@ struct Problem {
     int32_t nr_levels;
     uint32_t capacity;
     int32_t cap_is_pow2;
-    int32_t width;        // 2 * (L + extra): row length of features / gradients
+    int32_t nr_feat;      // F: features per level, 2, 4 or 8
+    int32_t width;        // F * (L + extra): row length of features / gradients
     int32_t level_begin;  // levels [level_begin, level_end) are processed
     int32_t level_end;
     int32_t extra_levels; // concat rows

@@ -94,7 +94,8 @@ def sigmas_of(case: dict) -> np.ndarray:
 
 
 def extra_levels(case: dict) -> int:
-    return (case["pos_dim"] + 1) // 2 if case.get("concat") else 0
+    feat = case.get("feat", 2)
+    return (case["pos_dim"] + feat - 1) // feat if case.get("concat") else 0
 
 
 def make_inputs(name: str) -> dict:
@@ -102,11 +103,12 @@ def make_inputs(name: str) -> dict:
     c = CASES[name]
     k = zlib.crc32(name.encode()) % 100000  # seed offset depends on the name only, not on the other cases
     d, cap, nl, n = c["pos_dim"], c["capacity"], c["nr_levels"], c["n"]
-    width = 2 * (nl + extra_levels(c))
+    feat = c.get("feat", 2)  # features per level; the reference (and every fixture) uses 2
+    width = feat * (nl + extra_levels(c))
     lo, hi = c["box"]
     inputs = {
         "sigmas": sigmas_of(c),
-        "table": uniform((nl, cap, 2), 1000000 + k, -c["table"], c["table"]),
+        "table": uniform((nl, cap, feat), 1000000 + k, -c["table"], c["table"]),
         "shift": normal((nl, d), 2000000 + k, 10.0),
         "positions": uniform((n, d), 3000000 + k, lo, hi),
         "grad_out": normal((n, width), 4000000 + k, 1.0),

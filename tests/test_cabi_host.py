@@ -37,6 +37,8 @@ def test_library_exports_every_declared_symbol(nat):
 
 def test_extra_levels(nat):
     assert [nat.extra_levels(d, True) for d in range(2, 8)] == [1, 2, 2, 3, 3, 4]
+    assert [nat.extra_levels(d, True, 4) for d in range(2, 8)] == [1, 1, 1, 2, 2, 2]
+    assert nat.extra_levels(7, True, 8) == 1
     assert nat.extra_levels(3, False) == 0
 
 
@@ -62,9 +64,9 @@ def test_argument_validation_without_gpu(nat):
     ins = nat.PermutoInputs(10, 8, 3, 1, 8, 8, 8, 8)
     assert lib.permuto_forward(C.byref(cfg), C.byref(ins), C.c_void_p(8), None) == nat.PERMUTO_ERR_UNSUPPORTED
     assert "pos_dim must be 2,3,4,5,6 or 7" in nat.last_error()
-    cfg = nat.PermutoConfig(3, 4, 4, 1024, 0, 1.0, 0)
+    cfg = nat.PermutoConfig(3, 3, 4, 1024, 0, 1.0, 0)
     assert lib.permuto_forward(C.byref(cfg), C.byref(ins), C.c_void_p(8), None) == nat.PERMUTO_ERR_UNSUPPORTED
-    assert "nr_feat_per_level must be 2" in nat.last_error()
+    assert "nr_feat_per_level must be 2, 4 or 8" in nat.last_error()
     cfg = nat.PermutoConfig(3, 2, 4, 1024, 0, 1.0, 0)
     ins0 = nat.PermutoInputs(0, 8, 3, 1, 8, 8, 8, 8)
     assert lib.permuto_forward(C.byref(cfg), C.byref(ins0), C.c_void_p(8), None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
@@ -86,8 +88,8 @@ def test_argument_validation_without_gpu(nat):
 def test_wrapper_rejects_what_the_reference_rejects(nat):
     shift = torch.zeros(4, 3)
     fx = nat.EncodingFixedParams(3, 1024, 4, 2, np.geomspace(1, 0.1, 4), shift, False, 1.0)
-    with pytest.raises(RuntimeError, match="nr_feat_per_level must be 2"):
-        nat.EncodingWrapper.create(3, 4, fx)
+    with pytest.raises(RuntimeError, match="nr_feat_per_level must be 2, 4 or 8"):
+        nat.EncodingWrapper.create(3, 3, fx)
     with pytest.raises(RuntimeError, match="pos_dim must be"):
         nat.EncodingWrapper.create(8, 2, fx)
     enc = nat.EncodingWrapper.create(3, 2, fx)

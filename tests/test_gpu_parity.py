@@ -39,9 +39,10 @@ def table_bound(table_abs):
 
 def make_encoding(nat, c, inp):
     shift = T(inp["shift"])
-    fx = nat.EncodingFixedParams(c["pos_dim"], c["capacity"], c["nr_levels"], 2, inp["sigmas"], shift,
+    feat = c.get("feat", 2)
+    fx = nat.EncodingFixedParams(c["pos_dim"], c["capacity"], c["nr_levels"], feat, inp["sigmas"], shift,
                                  c.get("concat", False), c.get("points_scaling", 1.0))
-    return nat.EncodingWrapper.create(c["pos_dim"], 2, fx), fx
+    return nat.EncodingWrapper.create(c["pos_dim"], feat, fx), fx
 
 
 def check_all(nat, oracle, c, inp, golden=None, parts=("forward", "backward", "double")):
@@ -447,3 +448,42 @@ def test_many_dimensions_non_power_of_two_levels(nat, oracle):
     finally:
         del cases.CASES["edge_d5"]
     check_all(nat, oracle, c, inp)
+
+
+@pytest.mark.parametrize("feat", [4, 8])
+@pytest.mark.parametrize("d", [2, 3, 4, 6])
+def test_wider_features_against_oracle(nat, oracle, feat, d):
+    """4 and 8 features per level (the reference lists them as not yet implemented): same
+    geometry, wider table entries.  Checked against the oracle generalised the same way; level
+    counts that are not multiples of the step, a non-power-of-two capacity, concat columns."""
+    c = dict(pos_dim=d, capacity=50021 if d == 3 else 2 ** 15, nr_levels=7 if feat == 4 else 5, sigma=(1.0, 1e-3),
+             n=10007, box=(-1.0, 1.0), table=1.0, feat=feat, concat=(d == 3), points_scaling=2.0)
+    name = f"wide_f{feat}_d{d}"
+    cases.CASES[name] = c
+    try:
+        inp = cases.make_inputs(name)
+    finally:
+        del cases.CASES[name]
+    check_all(nat, oracle, c, inp)
+
+
+@pytest.mark.parametrize("feat", [4, 8])
+def test_wider_features_module_and_full_size_identity(nat, feat):
+    """Module surface with nr_feat_per_level 4 / 8 and the linearity identity at 2^20 points."""
+    from permutohedral_encoding_b200 import PermutoEncoding
+    L = 48 // feat
+    torch.manual_seed(1)
+    m = PermutoEncoding(3, 2 ** 18, L, feat, np.geomspace(1.0, 1e-4, L))
+    assert m.lattice_values.shape == (L, 2 ** 18, feat) and m.output_dims() == 48
+    with torch.no_grad():
+        m.lattice_values.uniform_(-1.0, 1.0)
+    pos = torch.rand(2 ** 20, 3, device=DEV)
+    go = torch.randn(2 ** 20, 48, device=DEV)
+    out = m(pos)
+    assert out.shape == (2 ** 20, 48)
+    out.backward(go)
+    tg = m.lattice_values.grad
+    lhs = (go.double() * out.detach().double()).sum().item()
+    rhs = (tg.double() * m.lattice_values.detach().double()).sum().item()
+    scale = (go.double().abs() * out.detach().double().abs()).sum().item()
+    assert abs(lhs - rhs) <= 1e-5 * scale

@@ -154,3 +154,32 @@ def test_oracle_identities(oracle):
     y = float((db["table_grad"].astype(np.float64) * inp["table"]).sum())
     z = float((db["grad_grad_out"].astype(np.float64) * inp["grad_out"]).sum())
     assert abs(x - y) <= 1e-4 * (abs(x) + 1) and abs(x - z) <= 1e-4 * (abs(x) + 1)
+
+
+@pytest.mark.parametrize("feat", [4, 8])
+def test_oracle_identities_wider_features(oracle, feat):
+    """The oracle's generalisation to 4 / 8 features per level (no reference fixtures exist for
+    them): linearity in the table, bilinearity of the position gradient, and agreement of the
+    first two features with a 2-feature table holding the same values."""
+    c = dict(pos_dim=3, capacity=4099, nr_levels=5, sigma=(1.0, 1e-2), n=500, box=(0.0, 1.0), table=1.0, feat=feat)
+    cases.CASES["tmp_wide"] = c
+    try:
+        inp = cases.make_inputs("tmp_wide")
+    finally:
+        del cases.CASES["tmp_wide"]
+    scale = oracle.scale_factor(inp["sigmas"], 3)
+    a = (inp["positions"], inp["table"], scale, inp["shift"], inp["anneal"])
+    out = oracle.forward(*a)
+    assert out.shape == (500, 5 * feat)
+    narrow = oracle.forward(inp["positions"], np.ascontiguousarray(inp["table"][:, :, :2]), scale, inp["shift"],
+                            inp["anneal"])
+    np.testing.assert_array_equal(out.reshape(500, 5, feat)[:, :, :2].reshape(500, 10), narrow)
+    bw = oracle.backward(*a, inp["grad_out"], need_pos=True)
+    lhs = float((inp["grad_out"].astype(np.float64) * out).sum())
+    rhs = float((bw["table_grad"].astype(np.float64) * inp["table"]).sum())
+    assert abs(lhs - rhs) <= 1e-5 * (abs(lhs) + 1)
+    db = oracle.double_backward(*a, inp["dpg"], inp["grad_out"])
+    x = float((inp["dpg"].astype(np.float64) * bw["pos_grad"]).sum())
+    y = float((db["table_grad"].astype(np.float64) * inp["table"]).sum())
+    z = float((db["grad_grad_out"].astype(np.float64) * inp["grad_out"]).sum())
+    assert abs(x - y) <= 1e-4 * (abs(x) + 1) and abs(x - z) <= 1e-4 * (abs(x) + 1)
