@@ -61,6 +61,10 @@ if ARGS.impl == "reference" and WORLD > 1:
 else:
     LOCAL_DEVICE = LOCAL_RANK
 
+if ARGS.impl == "ours" and LOCAL_RANK == 0:
+    from permutohedral_encoding_b200 import build as _ext_build  # noqa: E402
+    _ext_build.build()  # no-op when the library is newer than its sources
+
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402

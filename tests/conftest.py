@@ -15,6 +15,15 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 
 
+def pytest_sessionstart(session):
+    """Compile the CUDA extension (nvcc cross-compiles without a GPU) and the C checker if they are
+    missing or older than their sources, so that a fresh checkout can run the suite directly."""
+    from permutohedral_encoding_b200 import build as ext_build
+    ext_build.build()
+    from oracle import permuto_oracle
+    permuto_oracle.build()
+
+
 def pytest_collection_modifyitems(config, items):
     # every test in a test_gpu_* / test_zz_* file needs the device even when the mark was forgotten
     for item in items:
