@@ -39,6 +39,11 @@ constexpr int D = PERMUTO_DIM;
 #ifndef PERMUTO_MIN_BLOCKS_GATHER_ONLY
 #define PERMUTO_MIN_BLOCKS_GATHER_ONLY (PERMUTO_DIM <= 4 ? 5 : 4)  // 5 spills and loses from pos_dim 5 up
 #endif
+// The forward kernel is bound by the LSU pipe, not by instruction-level parallelism: at 60
+// registers (what a cap of 64 invites) it runs 4 % slower than at 32 with twice the resident warps.
+#ifndef PERMUTO_MIN_BLOCKS_FORWARD
+#define PERMUTO_MIN_BLOCKS_FORWARD (PERMUTO_DIM <= 3 ? 8 : (PERMUTO_DIM == 4 ? 6 : 4))
+#endif
 constexpr int kThreads = PERMUTO_THREADS;
 // wider table entries keep more addends live per vertex: leave them more registers
 constexpr int min_blocks(int feats, bool gather_only) {
@@ -178,7 +183,7 @@ __device__ __forceinline__ void store_row_segment(const Problem& p, float* rows,
 // forward
 // ------------------------------------------------------------------------------------------
 template <int F, int LPS>
-__global__ void __launch_bounds__(kThreads, min_blocks(F, false)) forward_kernel(const ForwardArgs a) {
+__global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD : min_blocks(F, false))) forward_kernel(const ForwardArgs a) {
     const Problem& p = a.p;
     const int64_t n = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (n >= p.n_points) return;
