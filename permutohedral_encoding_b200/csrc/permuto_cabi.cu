@@ -38,7 +38,8 @@ int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::
     if (cfg->nr_feat_per_level != 2 && cfg->nr_feat_per_level != 4 && cfg->nr_feat_per_level != 8)
         return fail(PERMUTO_ERR_UNSUPPORTED, "Encoding: nr_feat_per_level must be 2, 4 or 8 (got %d)",
                     cfg->nr_feat_per_level);
-    if (cfg->nr_levels < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "nr_levels must be >= 1");
+    if (cfg->nr_levels < 1 || cfg->nr_levels > 65535)
+        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "nr_levels must be in 1..65535 (got %d)", cfg->nr_levels);
     if (cfg->capacity < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "capacity must be >= 1");
     if (in->nr_positions < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "Why do we have 0 points");
     if (in->nr_positions > (int64_t)0x7fffffff)
