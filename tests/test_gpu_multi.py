@@ -73,3 +73,30 @@ def test_sharded_step_matches_single_gpu(tmp_path, use_multimem):
     mp.spawn(_worker, args=(2, port, str(tmp_path), use_multimem), nprocs=2, join=True)
     for r in range(2):
         assert torch.load(tmp_path / f"r{r}.pt")["ok"] == (True, True, True)
+
+
+def test_module_on_a_device_that_is_not_current():
+    """The reference pins cuda:0; here an encoding lives on whatever device its parameters are on,
+    also when another device is current on the calling thread."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    sys.path.insert(0, ROOT)
+    from permutohedral_encoding_b200 import PermutoEncoding
+    sig = np.geomspace(1.0, 1e-2, 8)
+    torch.manual_seed(3)
+    with torch.cuda.device(0):
+        m0 = PermutoEncoding(3, 2 ** 12, 8, 2, sig)
+    pos = torch.rand(5000, 3)
+    go = torch.randn(5000, 16)
+    out0 = m0(pos.cuda(0))
+    out0.backward(go.cuda(0))
+    m1 = PermutoEncoding(3, 2 ** 12, 8, 2, sig)
+    m1.load_state_dict(m0.state_dict())
+    m1 = m1.to("cuda:1")
+    torch.cuda.set_device(0)                       # cuda:0 stays current while cuda:1 is used
+    out1 = m1(pos.to("cuda:1"))
+    out1.backward(go.to("cuda:1"))
+    assert out1.device.index == 1 and m1.lattice_values.grad.device.index == 1
+    assert torch.equal(out1.cpu(), out0.cpu())
+    lvl = m0.lattice_values.grad.abs().amax(dim=(1, 2), keepdim=True).cpu()
+    assert torch.all((m1.lattice_values.grad.cpu() - m0.lattice_values.grad.cpu()).abs() <= 1e-4 * lvl + 1e-12)
