@@ -390,15 +390,21 @@ def main():
                             "algorithmic_bytes_per_launch": dom[2], "ms_per_launch": round(dom[1], 4),
                             "forward_kernel": {"ms": round(ms_f, 4), "achieved": round(bytes_f / (ms_f * 1e-3) / 1e9, 1)},
                             "backward_kernel": {"ms": round(ms_b, 4), "achieved": round(bytes_b / (ms_b * 1e-3) / 1e9, 1)}}
-        # the binding resource is the rate of random 8-byte accesses that reach L2, not HBM bytes:
-        # measured ceilings on B200 (independent random accesses over an L2-resident region)
+        # the binding resource is the rate of random accesses that reach L2, not HBM bytes: measure
+        # the device's ceilings for that pattern now (independent random accesses over an 8 MB region)
+        from permutohedral_encoding_b200 import probe
+        ceil_g = probe.measure("gather8" if F == 2 else "gather16", device=device) / 1e9
+        ceil_r = probe.measure("red_v2" if F == 2 else "red_v4", device=device) / 1e9
         visits = n_local * L * V
+        ops_per_visit = 2 if F == 8 else 1  # a 32-byte entry is two 16-byte operations
         line["roofline_l2_random_access"] = {
-            "forward_kernel": {"achieved_gather_per_s": round(visits / (ms_f * 1e-3) / 1e9, 1), "ceiling": 295.0,
-                               "unit": "G 8-byte gathers/s"},
-            "backward_kernel": {"achieved_red_per_s": round(visits / (ms_b * 1e-3) / 1e9, 1), "ceiling": 220.0,
-                                "unit": "G 8-byte vector reductions/s (before the in-warp merge)"},
-            "ceiling_source": "microbenchmark on this pool's B200, see profiles/"}
+            "forward_kernel": {"achieved": round(visits * ops_per_visit / (ms_f * 1e-3) / 1e9, 1), "ceiling": round(ceil_g, 1),
+                               "frac": round(visits * ops_per_visit / (ms_f * 1e-3) / 1e9 / ceil_g, 3),
+                               "unit": "G random gathers/s"},
+            "backward_kernel": {"achieved": round(visits * ops_per_visit / (ms_b * 1e-3) / 1e9, 1), "ceiling": round(ceil_r, 1),
+                                "frac": round(visits * ops_per_visit / (ms_b * 1e-3) / 1e9 / ceil_r, 3),
+                                "unit": "G vector reductions/s (counted before the in-warp merge)"},
+            "ceiling_source": "permuto_probe_random_access, measured in this run over an L2-resident 8 MB region"}
         if RANK == 0 and WORLD == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
     if WORLD > 1:

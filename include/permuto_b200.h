@@ -121,6 +121,15 @@ int permuto_double_backward(const permuto_config *cfg, const permuto_inputs *in,
 int permuto_debug_lattice(const permuto_config *cfg, const permuto_inputs *in, int32_t *keys,
                           int32_t *slots, float *bary, int32_t *rank, void *stream);
 
+/* Measurement aid with no counterpart in the reference: launches, from every SM at full
+ * occupancy, `accesses_per_thread` (a multiple of 4) independent random accesses per thread over
+ * the caller's region (device memory, 16-byte aligned, zero-filled by the caller; the reductions
+ * add zeros, so the region keeps its contents).  kind 0 = 8-byte gather, 1 = 16-byte gather,
+ * 2 = red.global.add.v2.f32, 3 = red.global.add.v4.f32.  The caller times the stream; the
+ * lattice kernels' achieved operations per second are compared with these ceilings. */
+int permuto_probe_random_access(int32_t kind, float *region, int64_t region_bytes, int32_t accesses_per_thread,
+                                int64_t *total_accesses, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,7 @@ PERMUTO_KEEP_POSITIONS_GRAD = 4
 EXPORTED_SYMBOLS = (
     "permuto_abi_version", "permuto_last_error", "permuto_extra_levels", "permuto_scale_factor",
     "permuto_forward", "permuto_backward", "permuto_double_backward", "permuto_debug_lattice",
+    "permuto_probe_random_access",
 )
 
 
@@ -74,6 +75,9 @@ def _load() -> C.CDLL:
                                             C.c_uint32, C.c_void_p]
     lib.permuto_debug_lattice.restype = C.c_int
     lib.permuto_debug_lattice.argtypes = [cfgp, inp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.permuto_probe_random_access.restype = C.c_int
+    lib.permuto_probe_random_access.argtypes = [C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.POINTER(C.c_int64),
+                                                C.c_void_p]
     if lib.permuto_abi_version() != 1:
         raise ImportError(f"{LIB_PATH}: ABI version {lib.permuto_abi_version()} != 1; rebuild the extension")
     return lib

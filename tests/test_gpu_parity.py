@@ -487,3 +487,19 @@ def test_wider_features_module_and_full_size_identity(nat, feat):
     rhs = (tg.double() * m.lattice_values.detach().double()).sum().item()
     scale = (go.double().abs() * out.detach().double().abs()).sum().item()
     assert abs(lhs - rhs) <= 1e-5 * scale
+
+
+def test_random_access_probe(nat):
+    """The ceiling probe runs, leaves its region untouched, and reports plausible rates."""
+    from permutohedral_encoding_b200 import probe
+    rates = probe.ceilings(4 << 20)
+    assert set(rates) == {"gather8", "gather16", "red_v2", "red_v4"}
+    assert all(20.0 < v < 5000.0 for v in rates.values()), rates
+    import ctypes as C
+    region = torch.zeros(1024, device=DEV)
+    assert nat.lib.permuto_probe_random_access(7, region.data_ptr(), 4096, 4, None, None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
+    assert nat.lib.permuto_probe_random_access(0, region.data_ptr(), 4096, 6, None, None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
+    total = C.c_int64(0)
+    nat.check(nat.lib.permuto_probe_random_access(2, region.data_ptr(), 4096, 8, C.byref(total), None))
+    torch.cuda.synchronize()
+    assert total.value > 0 and torch.count_nonzero(region) == 0
