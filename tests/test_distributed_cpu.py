@@ -76,3 +76,57 @@ def test_bucketed_allreduce_two_ranks(tmp_path):
     assert r0["bounds"] == (0, 501) and r1["bounds"] == (501, 1001)
     assert torch.equal(r0["sum"], r1["sum"])
     assert torch.allclose(r0["sum"], r0["full"], rtol=1e-4, atol=1e-4)
+
+
+class _FakeLattice:
+    """Stands in for the native wrapper on CPU: fills the requested level range of the gradient
+    buffer with a rank-dependent pattern, like a backward over that bucket would."""
+
+    def __init__(self, rank):
+        self.rank, self.calls, self.backward_hook = rank, [], None
+
+    def backward(self, input_struct, grad_features, lattice_grad_out=None, level_begin=None, level_end=None, zero=True,
+                 positions_grad_out=None):
+        self.calls.append((level_begin, level_end))
+        lattice_grad_out[level_begin:level_end] = float(self.rank + 1) * (1 + torch.arange(level_begin, level_end)
+                                                                          ).view(-1, 1, 1).float()
+        return lattice_grad_out, None
+
+
+class _FakeEncoding:
+    def __init__(self, rank, nr_levels):
+        self.nr_levels = nr_levels
+        self.lattice = _FakeLattice(rank)
+        self.lattice_values = torch.zeros(nr_levels, 8, 2)
+
+
+class _FakeInput:
+    def __init__(self, values):
+        self.m_lattice_values = values
+
+
+def _hook_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from permutohedral_encoding_b200.distributed import LatticeGradAllReduce
+    enc = _FakeEncoding(rank, 10)
+    hook = LatticeGradAllReduce(enc, nr_buckets=3, average=True, multimem="auto")   # gloo: falls back to all_reduce
+    assert hook._symm is None and enc.lattice.backward_hook is not None
+    grad, pos_grad = enc.lattice.backward_hook(enc.lattice, _FakeInput(enc.lattice_values), None)
+    torch.save({"grad": grad, "calls": enc.lattice.calls, "pos": pos_grad}, os.path.join(out_dir, f"h{rank}.pt"))
+    hook.remove()
+    assert enc.lattice.backward_hook is None
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gradient_hook_buckets_and_averages_two_ranks(tmp_path):
+    """The backward hook of the data-parallel helper on two gloo ranks with a stand-in for the
+    native backward: one call per bucket, bucket-wise all-reduce, mean over ranks."""
+    port = _free_port()
+    mp.spawn(_hook_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    h0, h1 = torch.load(tmp_path / "h0.pt"), torch.load(tmp_path / "h1.pt")
+    assert h0["calls"] == [(0, 4), (4, 8), (8, 10)] and h0["pos"] is None
+    want = 1.5 * (1 + torch.arange(10)).view(-1, 1, 1).float().expand(10, 8, 2)   # mean of 1x and 2x
+    assert torch.equal(h0["grad"], h1["grad"]) and torch.allclose(h0["grad"], want)
