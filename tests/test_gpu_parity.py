@@ -503,3 +503,34 @@ def test_random_access_probe(nat):
     nat.check(nat.lib.permuto_probe_random_access(2, region.data_ptr(), 4096, 8, C.byref(total), None))
     torch.cuda.synchronize()
     assert total.value > 0 and torch.count_nonzero(region) == 0
+
+
+def test_randomised_configurations(nat, oracle):
+    """Forty seeded random configurations (dimension, feature width, level count, capacity --
+    power of two or not --, point count around warp and block edges, box, window, concat) through
+    the full check against the oracle."""
+    rng = np.random.default_rng(2024)
+    for it in range(40):
+        d = int(rng.integers(2, 8))
+        feat = int(rng.choice([2, 2, 4, 8]))
+        cap = int(rng.choice([1, 7, 1000, 4096, 65536, 100003, 2 ** 17]))
+        lo = float(rng.choice([0.0, -1.0, -100.0, 5.0]))
+        c = dict(pos_dim=d, capacity=cap, nr_levels=int(rng.integers(1, 14)),
+                 sigma=(float(rng.choice([1.0, 3.0])), float(rng.choice([1.0, 1e-1, 1e-2, 1e-3]))),
+                 n=int(rng.choice([1, 2, 31, 32, 33, 255, 256, 257, 1000, 5000, 40000])),
+                 box=(lo, lo + float(rng.choice([1e-3, 1.0, 10.0]))), table=1.0, feat=feat,
+                 concat=bool(rng.integers(0, 2)), points_scaling=float(rng.choice([1.0, 0.25])))
+        if rng.integers(0, 3) == 0:
+            c["window_t"] = float(rng.uniform(0, 1))
+        name = f"random_{it}"
+        cases.CASES[name] = c
+        try:
+            inp = cases.make_inputs(name)
+        finally:
+            del cases.CASES[name]
+        # with a handful of slots the grad-grad features are cancellation noise (see the one-slot case)
+        parts = ("forward", "backward") if cap <= 7 else ("forward", "backward", "double")
+        try:
+            check_all(nat, oracle, c, inp, parts=parts)
+        except AssertionError as exc:
+            raise AssertionError(f"configuration {c}: {exc}") from exc
