@@ -61,9 +61,10 @@ if ARGS.impl == "reference" and WORLD > 1:
 else:
     LOCAL_DEVICE = LOCAL_RANK
 
-if ARGS.impl == "ours" and LOCAL_RANK == 0:
+if ARGS.impl == "ours" and WORLD == 1:
     from permutohedral_encoding_b200 import build as _ext_build  # noqa: E402
-    _ext_build.build()  # no-op when the library is newer than its sources
+    if not os.path.isfile(_ext_build.LIB_PATH):  # a fresh checkout; multi-rank runs expect it built already
+        _ext_build.build()
 
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
