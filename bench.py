@@ -1,29 +1,41 @@
 #!/usr/bin/env python
 """Benchmark of the permutohedral-encoding hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload train|sharded]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 One step = forward + backward into the lattice values over one batch of synthetic points
 (seeded; uniform points, N(0,1) upstream gradient -- the reference's performance script also
-uses synthetic uniform points).  Workloads:
+uses synthetic uniform points).  The headline workload is the same at every N, so that the
+per-N values form a scaling curve:
 
-  train    pos_dim 3, 24 levels, capacity 2^18, 2^20 points            (default for --gpus 1)
   sharded  pos_dim 3, 24 levels, capacity 2^19, 2^24 points per step split evenly over the
-           ranks, lattice replicated, all-reduce of the lattice gradient (default for N > 1)
+           ranks (strong scaling), lattice replicated, all-reduce of the lattice gradient for N > 1
+
+At N = 1 the line also carries one block per other configuration of the baseline, each timed the
+same way in both arms (``--impl ours`` and ``--impl reference``):
+
+  train                 pos_dim 3, 24 levels, capacity 2^18, 2^20 points, forward + backward
+  readme_forward        the same encoding, forward of 1000 points (latency per call)
+  eikonal               capacity 2^19, 2^19 points in [-1,1)^3: forward, d/dx with create_graph,
+                        loss on the gradient norm, double backward into the lattice values
+  dim4, dim6            pos_dim 4 / 6, 16 levels, capacity 2^20, 2^20 points, forward + backward
+  train_with_optimizer  the train step with MSE loss and an AdamW step on the table
+                        (the reference's examples/performance.py loop)
 
 Rank 0 prints ONE JSON line.  ``value`` is whole-job Mpoints/s with inputs resident in HBM,
-timed on the device with CUDA events (max over ranks); ``e2e`` is the same step driven from
-pinned host memory (host->device copy of the positions, forward, MSE loss, backward,
-device->host read of the loss) through the public module API.
+timed on the device with CUDA events (max over ranks, median over repeats of K steps);
+``e2e`` is the same step driven from pinned host memory (host->device copy of the positions,
+forward, MSE loss, backward, device->host read of the loss) through the public module API.
 
 ``--impl reference`` times the reference's own CUDA extension (oracle/_ref, rebuilt unmodified
 for sm_100; the reference has no CPU path) through the call sequence of its Python module,
-on the same workload; if that build is absent it falls back to the CPU restatement in oracle/.
+on the same workloads; if that build is absent it falls back to the CPU restatement in oracle/.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -38,14 +50,18 @@ sys.path.insert(0, ROOT)
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "train", "sharded", "train_f8"])
+    ap.add_argument("--workload", default="sharded", choices=["sharded", "train", "train_f8"])
     ap.add_argument("--buckets", type=int, default=2, help="level buckets of the overlapped all-reduce")
     ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "multimem"])
     ap.add_argument("--bucket-policy", default="halving", choices=["halving", "even"])
+    ap.add_argument("--copy-out", action="store_true", help="copy the reduced gradient out of the symmetric buffer")
+    ap.add_argument("--clear", default="inline", choices=["inline", "early"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-blocks", action="store_true", help="skip the per-configuration blocks at N = 1")
+    ap.add_argument("--min-timed-seconds", type=float, default=0.5)
     return ap.parse_args()
 
 
@@ -71,16 +87,32 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 WORKLOADS = {
-    "train": dict(pos_dim=3, nr_levels=24, capacity=2 ** 18, total_points=2 ** 20, sigma=(1.0, 1e-4)),
     "sharded": dict(pos_dim=3, nr_levels=24, capacity=2 ** 19, total_points=2 ** 24, sigma=(1.0, 1e-4)),
+    "train": dict(pos_dim=3, nr_levels=24, capacity=2 ** 18, total_points=2 ** 20, sigma=(1.0, 1e-4)),
+    "readme_forward": dict(pos_dim=3, nr_levels=24, capacity=2 ** 18, total_points=1000, sigma=(1.0, 1e-4)),
+    "eikonal": dict(pos_dim=3, nr_levels=24, capacity=2 ** 19, total_points=2 ** 19, sigma=(1.0, 1e-4), box=(-1.0, 1.0)),
+    "dim4": dict(pos_dim=4, nr_levels=16, capacity=2 ** 20, total_points=2 ** 20, sigma=(1.0, 1e-3)),
+    "dim6": dict(pos_dim=6, nr_levels=16, capacity=2 ** 20, total_points=2 ** 20, sigma=(1.0, 1e-3)),
     # not a reference configuration (it has no 8-feature levels): the same 48 outputs from 6 levels of
     # 8 features, every table access a whole 32-byte sector
     "train_f8": dict(pos_dim=3, nr_levels=6, nr_feat=8, capacity=2 ** 18, total_points=2 ** 20, sigma=(1.0, 1e-4)),
 }
+METRIC = "fwd+bwd throughput, pos_dim=3, 24 levels"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch on the "train" workload, from the ncu
-# capture summarised in profiles/train_step_forward_backward_kernels.txt; None = not captured.
-NCU_TRAFFIC_BYTES = {"train": {"backward_kernel": 245.0e6, "forward_kernel": 202.5e6}, "sharded": None}
+
+def load_json(path):
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
+
+
+PEAKS = load_json(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+HBM_PEAK = float(PEAKS.get("hbm_gbs", 6650.0))
+PEAK_SOURCE = "measured (MEASURED_PEAKS.json)" if PEAKS else "fallback (6650 GB/s)"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in profiles/
+NCU_TRAFFIC = load_json(os.path.join(ROOT, "profiles", "ncu_dram_traffic.json"))
 
 
 class ClockSampler:
@@ -136,7 +168,8 @@ def make_data(w, n_local, seed, device):
     table = ((torch.rand((L, cap, w.get("nr_feat", 2)), generator=gen) * 2 - 1) * 1e-4)
     shift = torch.randn((L, d), generator=gen) * 10
     gen = torch.Generator(device="cpu").manual_seed(seed)
-    pos_host = torch.rand((n_local, d), generator=gen).pin_memory()
+    lo, hi = w.get("box", (0.0, 1.0))
+    pos_host = (torch.rand((n_local, d), generator=gen) * (hi - lo) + lo).pin_memory()
     return table.to(device), shift.to(device), pos_host
 
 
@@ -147,8 +180,9 @@ def device_randn(shape, seed, device):
 
 class OursStep:
     """forward + backward through the public module; the all-reduce hook is installed for N > 1."""
+    impl = "ours"
 
-    def __init__(self, w, table, shift, device, world, buckets):
+    def __init__(self, w, table, shift, device, world, buckets=2):
         from permutohedral_encoding_b200 import PermutoEncoding
         from permutohedral_encoding_b200.distributed import LatticeGradAllReduce
         sig = np.geomspace(w["sigma"][0], w["sigma"][1], w["nr_levels"])
@@ -157,10 +191,18 @@ class OursStep:
             self.m.lattice_values.copy_(table)
             self.m.random_shift_per_level.copy_(shift)
         mm = {"auto": "auto", "nccl": False, "multimem": True}[ARGS.collective]
-        self.hook = LatticeGradAllReduce(self.m, nr_buckets=buckets, policy=ARGS.bucket_policy, multimem=mm) \
-            if world > 1 else None
+        self.hook = LatticeGradAllReduce(self.m, nr_buckets=buckets, policy=ARGS.bucket_policy, multimem=mm,
+                                         copy_out=ARGS.copy_out, clear=ARGS.clear) if world > 1 else None
         self.collective = None if self.hook is None else ("multimem" if self.hook._symm is not None else "nccl")
         self.launches_per_step = 2 if world == 1 else 1 + len(self.hook.buckets)
+        self.opt = None
+
+    @property
+    def values(self):
+        return self.m.lattice_values
+
+    def encode(self, pos):
+        return self.m(pos)
 
     def step(self, pos, grad_out):
         self.m.lattice_values.grad = None
@@ -168,14 +210,10 @@ class OursStep:
         out.backward(grad_out)
         return out
 
-    def e2e_step(self, feeder, pos_host, target):
-        self.m.lattice_values.grad = None
-        pos = feeder.next()          # this step's positions (their copy was started one step ahead)
-        feeder.submit(pos_host)      # the next step's host->device copy runs beside this step
-        out = self.m(pos)
-        loss = torch.nn.functional.mse_loss(out, target.expand_as(out))
-        loss.backward()
-        return loss.item()
+    def make_optimizer(self):
+        from permutohedral_encoding_b200.optim import LatticeAdamW
+        self.opt = LatticeAdamW([self.m.lattice_values], lr=1e-3, betas=(0.9, 0.99), eps=1e-15, weight_decay=0.0,
+                                skip_untouched=True)
 
     def kernels(self, pos, grad_out):
         from permutohedral_encoding_b200 import _native as nat
@@ -187,8 +225,9 @@ class OursStep:
 
 class ReferenceStep:
     """The reference's CUDA extension driven like its Python module; all-reduce appended for N > 1."""
+    impl = "reference"
 
-    def __init__(self, w, table, shift, device, world):
+    def __init__(self, w, table, shift, device, world, buckets=None):
         from oracle import ref_shim
         sig = np.geomspace(w["sigma"][0], w["sigma"][1], w["nr_levels"])
         self.enc = ref_shim.RefEncoding(w["pos_dim"], w["capacity"], w["nr_levels"], sig, shift)
@@ -196,6 +235,15 @@ class ReferenceStep:
         self.window = torch.ones(w["nr_levels"], device=device)
         self.world = world
         self.launches_per_step = 0
+        self.collective = "nccl" if world > 1 else None
+        self.opt = None
+
+    @property
+    def values(self):
+        return self.table
+
+    def encode(self, pos):
+        return self.enc(self.table, pos, self.window)
 
     def step(self, pos, grad_out):
         self.table.grad = None
@@ -205,29 +253,48 @@ class ReferenceStep:
             dist.all_reduce(self.table.grad)
         return out
 
-    def e2e_step(self, feeder, pos_host, target):
-        self.table.grad = None
-        pos = feeder.next()
-        feeder.submit(pos_host)
-        out = self.enc(self.table, pos, self.window)
-        loss = torch.nn.functional.mse_loss(out, target.expand_as(out))
-        loss.backward()
-        if self.world > 1:
-            dist.all_reduce(self.table.grad)
-        return loss.item()
+    def make_optimizer(self):  # examples/performance.py:161
+        self.opt = torch.optim.AdamW([self.table], amsgrad=False, betas=(0.9, 0.99), eps=1e-15, weight_decay=0.0, lr=1e-3)
 
 
-def timed(fn, steps, warmup, sync):
-    for _ in range(warmup):
-        fn()
-    sync()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        fn()
-    b.record()
-    sync()
-    return a.elapsed_time(b) / steps  # ms per step
+def e2e_step(runner, feeder, pos_host, target):
+    runner.values.grad = None
+    pos = feeder.next()          # this step's positions (their copy was started one step ahead)
+    feeder.submit(pos_host)      # the next step's host->device copy runs beside this step
+    out = runner.encode(pos)
+    loss = torch.nn.functional.mse_loss(out, target.expand_as(out))
+    loss.backward()
+    if runner.impl == "reference" and WORLD > 1:
+        dist.all_reduce(runner.values.grad)
+    return loss.item()
+
+
+def eikonal_step(runner, pos, w_vec):
+    """PermutoSDF's eikonal term: y = F w, g = dy/dx (create_graph), loss = mean((|g| - 1)^2)."""
+    runner.values.grad = None
+    x = pos.detach().requires_grad_(True)
+    y = runner.encode(x) @ w_vec
+    (g,) = torch.autograd.grad(y.sum(), x, create_graph=True)
+    loss = ((g.norm(dim=1) - 1.0) ** 2).mean()
+    loss.backward()
+    return loss
+
+
+def optimizer_step(runner, pos):
+    """The reference's training loop (examples/performance.py:96-101)."""
+    pred = runner.encode(pos)
+    loss = ((pred - 10) ** 2).mean()
+    runner.opt.zero_grad()
+    loss.backward()
+    runner.opt.step()
+    return loss
+
+
+def sync_all():
+    torch.cuda.synchronize()
+    if WORLD > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
 
 
 def max_over_ranks(x, device):
@@ -236,6 +303,35 @@ def max_over_ranks(x, device):
     t = torch.tensor([x], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return t.item()
+
+
+def timed(fn, steps, warmup, device, min_seconds=None, sync=None):
+    """ms per step: `warmup` untimed steps, then repeats of exactly `steps` steps, each bracketed
+    by a synchronize (and a barrier for N > 1) on both sides and timed with CUDA events on the
+    current stream; a repeat's time is the max over ranks; the median over the repeats is
+    returned.  The number of repeats is chosen from the first one so that about `min_seconds` are
+    timed in total (every rank derives it from the same max-over-ranks value)."""
+    sync = sync or sync_all
+    min_seconds = ARGS.min_timed_seconds if min_seconds is None else min_seconds
+    for _ in range(warmup):
+        fn()
+    samples, repeats = [], 1
+    while len(samples) < repeats:
+        sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        sync()
+        samples.append(max_over_ranks(a.elapsed_time(b) / steps, device))
+        if len(samples) == 1:
+            repeats = int(min(25, max(1, math.ceil(min_seconds * 1e3 / max(samples[0] * steps, 1e-3)))))
+    return statistics.median(samples), len(samples)
+
+
+def local_sync():
+    torch.cuda.synchronize()
 
 
 def cpu_baseline(w):
@@ -274,31 +370,171 @@ def cpu_baseline(w):
                       f"OpenMP over {cores} host threads), {elapsed:.1f} s"}
 
 
+def algorithmic_bytes(w, n, kind):
+    """Bytes an ideal implementation must move (independent of sector granularity): positions,
+    8-byte table entries gathered or scattered, feature rows, and the zero-init of the gradient table."""
+    d, L, cap, F = w["pos_dim"], w["nr_levels"], w["capacity"], w.get("nr_feat", 2)
+    V = d + 1
+    row, entries, table = 4 * L * F, 4 * L * V * F, 4 * L * cap * F
+    per_point = {"fwd": 4 * d + entries + row, "bwd_table": 4 * d + row + entries,
+                 "bwd_pos": 4 * d + row + entries + 4 * d, "dbl_table": 8 * d + row + entries}[kind]
+    return n * per_point + (table if kind in ("bwd_table", "dbl_table") else 0)
+
+
+def roofline_block(w, name, n_local, ms_f, ms_b, device, ceilings=None):
+    """HBM roofline of the slower kernel plus the rate of random accesses against the device's
+    ceilings for that pattern, which is what binds these kernels."""
+    d, L, F = w["pos_dim"], w["nr_levels"], w.get("nr_feat", 2)
+    bytes_f, bytes_b = algorithmic_bytes(w, n_local, "fwd"), algorithmic_bytes(w, n_local, "bwd_table")
+    dom = ("backward_kernel", ms_b, bytes_b) if ms_b >= ms_f else ("forward_kernel", ms_f, bytes_f)
+    ach = dom[2] / (dom[1] * 1e-3) / 1e9
+    traffic = (NCU_TRAFFIC.get(name) or {}).get(dom[0])
+    out = {"bound": "hbm", "kernel": dom[0], "achieved": round(ach, 1), "peak": HBM_PEAK, "unit": "GB/s",
+           "frac": round(ach / HBM_PEAK, 4), "traffic": traffic, "traffic_source": (NCU_TRAFFIC.get(name) or {}).get("source"),
+           "peak_source": PEAK_SOURCE, "algorithmic_bytes_per_launch": dom[2], "ms_per_launch": round(dom[1], 4),
+           "forward_kernel": {"ms": round(ms_f, 4), "achieved": round(bytes_f / (ms_f * 1e-3) / 1e9, 1)},
+           "backward_kernel": {"ms": round(ms_b, 4), "achieved": round(bytes_b / (ms_b * 1e-3) / 1e9, 1)}}
+    if ceilings:
+        visits = n_local * L * (d + 1) * (2 if F == 8 else 1)  # a 32-byte entry is two 16-byte operations
+        g, r = visits / (ms_f * 1e-3) / 1e9, visits / (ms_b * 1e-3) / 1e9
+        out["l2_random_access"] = {
+            "forward_kernel": {"achieved": round(g, 1), "ceiling": ceilings["gather"], "frac": round(g / ceilings["gather"], 3),
+                               "unit": "G random gathers/s"},
+            "backward_kernel": {"achieved": round(r, 1), "ceiling": ceilings["red"], "frac": round(r / ceilings["red"], 3),
+                                "unit": "G vector reductions/s (counted before the in-warp merge)"},
+            "ceiling_source": "permuto_probe_random_access, measured in this run over an L2-resident 8 MB region"}
+        out["frac_l2_ops"] = out["l2_random_access"][dom[0]]["frac"]
+        out["ceiling"] = out["l2_random_access"][dom[0]]["ceiling"]
+        out["binding"] = ("l2 random-access rate: the kernel moves 8-byte table entries whose 32-byte sectors stay in L2, "
+                          "so DRAM bytes are not what limits it; frac is kept for the HBM roofline")
+    return out
+
+
+def make_runner(impl, w, table, shift, device, world=1):
+    return (ReferenceStep if impl == "reference" else OursStep)(w, table, shift, device, world, ARGS.buckets)
+
+
+def block_train(impl, name, device, steps, ceilings):
+    """forward + backward into the table on one GPU; used for train, dim4, dim6."""
+    w = WORKLOADS[name]
+    n, L, F = w["total_points"], w["nr_levels"], w.get("nr_feat", 2)
+    table, shift, pos_host = make_data(w, n, 100, device)
+    pos = pos_host.to(device)
+    grad_out = device_randn((n, F * L), 200, device)
+    runner = make_runner(impl, w, table, shift, device)
+    ms, reps = timed(lambda: runner.step(pos, grad_out), steps, 3, device, 0.2, local_sync)
+    with torch.no_grad():
+        ms_fo, _ = timed(lambda: runner.encode(pos), steps, 3, device, 0.1, local_sync)
+    blk = {"value": round(n / ms / 1e3, 2), "unit": "Mpoints/s", "ms_per_step": round(ms, 4), "repeats": reps,
+           "forward_only": {"value": round(n / ms_fo / 1e3, 2), "ms_per_step": round(ms_fo, 4)},
+           "config": {k: v for k, v in w.items()}}
+    if impl == "ours":
+        fwd, bwd = runner.kernels(pos, grad_out)
+        ms_f, _ = timed(fwd, 20, 3, device, 0.05, local_sync)
+        ms_b, _ = timed(bwd, 20, 3, device, 0.05, local_sync)  # includes the memset of the gradient table
+        blk["roofline"] = roofline_block(w, name, n, ms_f, ms_b, device, ceilings)
+    return blk, runner, pos
+
+
+def block_readme_forward(impl, device):
+    w = WORKLOADS["readme_forward"]
+    n = w["total_points"]
+    table, shift, pos_host = make_data(w, n, 101, device)
+    pos = pos_host.to(device)
+    runner = make_runner(impl, w, table, shift, device)
+    with torch.no_grad():
+        ms, reps = timed(lambda: runner.encode(pos), 200, 20, device, 0.1, local_sync)
+        for _ in range(20):
+            runner.encode(pos)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(500):
+            runner.encode(pos)
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) / 500
+    return {"value": round(ms * 1e3, 2), "unit": "us per forward of 1000 points (CUDA events, back-to-back calls)",
+            "wall_us_per_call": round(wall * 1e6, 2), "higher_is_better": False, "repeats": reps,
+            "note": "host-dispatch bound: the kernel itself runs for a few microseconds"}
+
+
+def block_eikonal(impl, device, steps):
+    w = WORKLOADS["eikonal"]
+    n, L = w["total_points"], w["nr_levels"]
+    table, shift, pos_host = make_data(w, n, 102, device)
+    pos = pos_host.to(device)
+    gen = torch.Generator(device="cpu").manual_seed(5003)
+    w_vec = (torch.randn(2 * L, generator=gen) * (1.0 / 48) ** 0.5).to(device)
+    runner = make_runner(impl, w, table, shift, device)
+    ms, reps = timed(lambda: eikonal_step(runner, pos, w_vec), steps, 3, device, 0.2, local_sync)
+    total = algorithmic_bytes(w, n, "fwd") + algorithmic_bytes(w, n, "bwd_pos") + algorithmic_bytes(w, n, "dbl_table")
+    ach = total / (ms * 1e-3) / 1e9
+    return {"value": round(n / ms / 1e3, 2), "unit": "Mpoints/s", "ms_per_step": round(ms, 4), "repeats": reps,
+            "config": {k: v for k, v in w.items()},
+            "roofline": {"bound": "hbm", "what": "whole step: forward + position backward + double backward into the table "
+                                                 "(the autograd elementwise kernels between them are not counted)",
+                         "achieved": round(ach, 1), "peak": HBM_PEAK, "unit": "GB/s", "frac": round(ach / HBM_PEAK, 4),
+                         "algorithmic_bytes_per_step": total}}
+
+
+def block_optimizer(impl, runner, pos, device, steps):
+    runner.make_optimizer()
+    ms, reps = timed(lambda: optimizer_step(runner, pos), steps, 3, device, 0.2, local_sync)
+    n = pos.shape[0]
+    return {"value": round(n / ms / 1e3, 2), "unit": "Mpoints/s", "ms_per_step": round(ms, 4), "repeats": reps,
+            "what": "train workload: forward, loss = mean((pred - 10)^2), zero_grad, backward, AdamW step on the table "
+                    "(betas 0.9/0.99, eps 1e-15, no weight decay), as in the reference's examples/performance.py"}
+
+
+def allreduce_check(runner, pos, grad_out, device):
+    """Outside the timed region: the gradient the overlapped, bucketed all-reduce left in .grad
+    against a plain all-reduce of an un-hooked local backward.  Largest error relative to the
+    level's largest entry (atomics make each local gradient differ in the last bits from run to run)."""
+    m = runner.m
+    runner.step(pos, grad_out)
+    torch.cuda.synchronize()
+    hooked = m.lattice_values.grad.clone()
+    hook_fn, hook2 = m.lattice.backward_hook, m.lattice.double_backward_hook
+    m.lattice.backward_hook = m.lattice.double_backward_hook = None
+    try:
+        m.lattice_values.grad = None
+        m(pos).backward(grad_out)
+        plain = m.lattice_values.grad.clone()
+    finally:
+        m.lattice.backward_hook, m.lattice.double_backward_hook = hook_fn, hook2
+    dist.all_reduce(plain)
+    torch.cuda.synchronize()
+    lvl = plain.abs().amax(dim=(1, 2)).clamp_min(1e-30)
+    err = ((hooked - plain).abs().amax(dim=(1, 2)) / lvl).max()
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    m.lattice_values.grad = None
+    return {"max_rel_err_per_level": float(err.item()), "tolerance": 1e-4, "ok": bool(err.item() <= 1e-4),
+            "what": "hooked bucketed all-reduce vs dist.all_reduce of a plain local backward, max over levels and ranks"}
+
+
+def reference_cpu_line(name, w):
+    cb = cpu_baseline(w)
+    return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "Mpoints/s", "n_gpus": ARGS.gpus,
+            "steps": 1, "warmup": 0, "higher_is_better": True, "ms_per_step": None, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": name, **w},
+            "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "Mpoints/s", "h2d_bytes_per_step": 0,
+                                        "d2h_bytes_per_step": 0},
+            "note": "reference CUDA extension build absent: CPU restatement timed instead"}
+
+
 def main():
     args = ARGS
-    name = args.workload or ("train" if args.gpus == 1 else "sharded")
+    name = args.workload
     w = WORKLOADS[name]
-    d, L, cap = w["pos_dim"], w["nr_levels"], w["capacity"]
-    use_ref_ext = False
+    d, L = w["pos_dim"], w["nr_levels"]
     if args.impl == "reference" and w.get("nr_feat", 2) != 2:
         if RANK == 0:
             print(json.dumps({"impl": "reference", "unavailable": "the reference implements nr_feat_per_level == 2 only"}))
         return 0
     if args.impl == "reference":
         from oracle import ref_shim
-        use_ref_ext = ref_shim.available() and torch.cuda.is_available()
-        if not use_ref_ext:
-            if RANK != 0:
-                return 0
-            cb = cpu_baseline(w)
-            line = {"impl": "reference", "metric": "fwd+bwd throughput, pos_dim=3, 24 levels", "value": cb["value"],
-                    "unit": "Mpoints/s", "n_gpus": args.gpus, "steps": 1, "warmup": 0, "higher_is_better": True,
-                    "ms_per_step": None, "scaling": "strong" if name == "sharded" else "weak", "vs_baseline": None,
-                    "dtype": "f32", "data": "synthetic", "config": {"workload": name, **w},
-                    "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "Mpoints/s", "h2d_bytes_per_step": 0,
-                                                "d2h_bytes_per_step": 0},
-                    "note": "reference CUDA extension build absent: CPU restatement timed instead"}
-            print(json.dumps(line))
+        if not (ref_shim.available() and torch.cuda.is_available()):
+            if RANK == 0:
+                print(json.dumps(reference_cpu_line(name, w)))
             return 0
 
     if not torch.cuda.is_available():
@@ -319,41 +555,34 @@ def main():
     F = w.get("nr_feat", 2)
     grad_out = device_randn((n_local, F * L), 200 + RANK, device)
     target = torch.full((1, 1), 0.3, device=device)
-
-    if args.impl == "reference":
-        runner = ReferenceStep(w, table, shift, device, WORLD)
-    else:
-        runner = OursStep(w, table, shift, device, WORLD, args.buckets)
-
-    def sync():
-        torch.cuda.synchronize()
-        if WORLD > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    runner = make_runner(args.impl, w, table, shift, device, WORLD)
 
     sampler = ClockSampler(LOCAL_RANK) if RANK == 0 else None
-    ms = max_over_ranks(timed(lambda: runner.step(pos, grad_out), args.steps, args.warmup, sync), device)
+    ms, repeats = timed(lambda: runner.step(pos, grad_out), args.steps, args.warmup, device)
     clocks = sampler.stop() if sampler else None
     e2e_steps = max(3, min(args.steps, 20))
     from permutohedral_encoding_b200.host_feed import HostPointFeeder
     feeder = HostPointFeeder(device)
     feeder.submit(pos_host)
-    ms_e2e = max_over_ranks(timed(lambda: runner.e2e_step(feeder, pos_host, target), e2e_steps, 3, sync), device)
+    ms_e2e, _ = timed(lambda: e2e_step(runner, feeder, pos_host, target), e2e_steps, 3, device, 0.2)
 
+    parallelism = f"dp{args.gpus}: points sharded, lattice replicated"
+    if WORLD > 1:
+        nr_buckets = len(runner.hook.buckets) if args.impl == "ours" else 1
+        parallelism += f", all-reduce of the lattice gradient in {nr_buckets} level bucket(s) ({runner.collective})"
     line = {
-        "metric": "fwd+bwd throughput, pos_dim=3, 24 levels",
+        "metric": METRIC,
         "value": round(total / ms / 1e3, 2), "unit": "Mpoints/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
-        "scaling": "strong" if name == "sharded" else "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "repeats": repeats, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, **{k: v for k, v in w.items()}, "points_per_gpu": n_local,
-                   "timing": "inputs larger than L2 (features and their gradient are 48*4 B per point)",
-                   "parallelism": f"dp{args.gpus}: points sharded, lattice replicated"
-                                  + (f", all-reduce of the lattice gradient in {args.buckets} level bucket(s) "
-                                     f"({getattr(runner, 'collective', 'nccl')})" if WORLD > 1 else "")},
+                   "timing": "inputs larger than L2 (features and their gradient are 48*4 B per point); "
+                             f"median of {repeats} repeat(s) of {args.steps} steps, max over ranks",
+                   "parallelism": parallelism},
         "e2e": {"value": round(total / ms_e2e / 1e3, 2), "unit": "Mpoints/s", "h2d_bytes_per_step": n_local * d * 4,
                 "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e, 4),
-                "what": "every step: pinned host positions -> device (double-buffered, copied beside the previous step), module forward, MSE loss, backward, loss.item()"},
+                "what": "every step: pinned host positions -> device (double-buffered, copied beside the previous step), "
+                        "module forward, MSE loss, backward, loss.item()"},
         "clocks": clocks,
     }
     if args.impl == "reference":
@@ -362,52 +591,41 @@ def main():
         line["cpu_baseline"] = {"value": line["value"], "unit": "Mpoints/s", "cores": 0, "kind": "reference",
                                 "sample": "the reference has no CPU path: its own CUDA extension (oracle/_ref, "
                                           "unmodified sources rebuilt for sm_100) on the full workload, on the GPU"}
-        line["e2e"] = {"value": line["e2e"]["value"], "unit": "Mpoints/s", "h2d_bytes_per_step": n_local * d * 4,
-                       "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e, 4)}
     else:
-        line["gpu_launches"] = runner.launches_per_step * args.steps
+        line["gpu_launches"] = runner.launches_per_step * args.steps * repeats
         with torch.no_grad():
-            ms_fo = max_over_ranks(timed(lambda: runner.m(pos), max(5, min(args.steps, 30)), 3, sync), device)
+            ms_fo, _ = timed(lambda: runner.encode(pos), max(5, min(args.steps, 30)), 3, device, 0.2)
         line["forward_only"] = {"value": round(total / ms_fo / 1e3, 2), "unit": "Mpoints/s", "ms_per_step": round(ms_fo, 4),
                                 "what": "module forward alone, inputs resident"}
         # kernel-only durations on the launching stream, for the roofline of the dominant kernel
         fwd, bwd = runner.kernels(pos, grad_out)
-        ms_f = timed(fwd, 20, 3, torch.cuda.synchronize)
-        ms_b = timed(bwd, 20, 3, torch.cuda.synchronize)  # includes the memset of the gradient slices
-        V = d + 1
-        bytes_f = n_local * (4 * d + 4 * L * V * F + 4 * L * F)
-        bytes_b = n_local * (4 * d + 4 * L * F + 4 * L * V * F) + 4 * L * cap * F
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except OSError:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        dom = ("backward_kernel", ms_b, bytes_b) if ms_b >= ms_f else ("forward_kernel", ms_f, bytes_f)
-        ach = dom[2] / (dom[1] * 1e-3) / 1e9
-        line["roofline"] = {"bound": "hbm", "kernel": dom[0], "achieved": round(ach, 1), "peak": peak, "unit": "GB/s",
-                            "frac": round(ach / peak, 4), "traffic": (NCU_TRAFFIC_BYTES.get(name) or {}).get(dom[0]),
-                            "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
-                            "algorithmic_bytes_per_launch": dom[2], "ms_per_launch": round(dom[1], 4),
-                            "forward_kernel": {"ms": round(ms_f, 4), "achieved": round(bytes_f / (ms_f * 1e-3) / 1e9, 1)},
-                            "backward_kernel": {"ms": round(ms_b, 4), "achieved": round(bytes_b / (ms_b * 1e-3) / 1e9, 1)}}
+        ms_f, _ = timed(fwd, 20, 3, device, 0.05, local_sync)
+        ms_b, _ = timed(bwd, 20, 3, device, 0.05, local_sync)  # includes the memset of the gradient slices
         # the binding resource is the rate of random accesses that reach L2, not HBM bytes: measure
         # the device's ceilings for that pattern now (independent random accesses over an 8 MB region)
         from permutohedral_encoding_b200 import probe
-        ceil_g = probe.measure("gather8" if F == 2 else "gather16", device=device) / 1e9
-        ceil_r = probe.measure("red_v2" if F == 2 else "red_v4", device=device) / 1e9
-        visits = n_local * L * V
-        ops_per_visit = 2 if F == 8 else 1  # a 32-byte entry is two 16-byte operations
-        line["roofline_l2_random_access"] = {
-            "forward_kernel": {"achieved": round(visits * ops_per_visit / (ms_f * 1e-3) / 1e9, 1), "ceiling": round(ceil_g, 1),
-                               "frac": round(visits * ops_per_visit / (ms_f * 1e-3) / 1e9 / ceil_g, 3),
-                               "unit": "G random gathers/s"},
-            "backward_kernel": {"achieved": round(visits * ops_per_visit / (ms_b * 1e-3) / 1e9, 1), "ceiling": round(ceil_r, 1),
-                                "frac": round(visits * ops_per_visit / (ms_b * 1e-3) / 1e9 / ceil_r, 3),
-                                "unit": "G vector reductions/s (counted before the in-warp merge)"},
-            "ceiling_source": "permuto_probe_random_access, measured in this run over an L2-resident 8 MB region"}
-        if RANK == 0 and WORLD == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(w)
+        ceilings = {"gather": round(probe.measure("gather8" if F == 2 else "gather16", device=device) / 1e9, 1),
+                    "red": round(probe.measure("red_v2" if F == 2 else "red_v4", device=device) / 1e9, 1)}
+        line["roofline"] = roofline_block(w, name, n_local, ms_f, ms_b, device, ceilings)
+        if WORLD > 1:
+            line["allreduce_check"] = allreduce_check(runner, pos, grad_out, device)
+
+    if WORLD == 1 and not args.no_blocks and name == "sharded":
+        del runner, pos, grad_out, feeder
+        torch.cuda.empty_cache()
+        ceil2 = ceilings if args.impl == "ours" else None
+        blk, r2, p2 = block_train(args.impl, "train", device, args.steps, ceil2)
+        line["train"] = blk
+        line["train_with_optimizer"] = block_optimizer(args.impl, r2, p2, device, args.steps)
+        del r2, p2
+        line["readme_forward"] = block_readme_forward(args.impl, device)
+        line["eikonal"] = block_eikonal(args.impl, device, args.steps)
+        for nm in ("dim4", "dim6"):
+            torch.cuda.empty_cache()
+            line[nm], r3, p3 = block_train(args.impl, nm, device, args.steps, None)
+            del r3, p3
+    if args.impl == "ours" and RANK == 0 and WORLD == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(w)
     if WORLD > 1:
         dist.barrier()
         dist.destroy_process_group()

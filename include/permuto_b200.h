@@ -11,7 +11,8 @@
  *
  * Layouts (all fp32, element strides):
  *   positions            [N, pos_dim]      arbitrary strides (pos_stride_n, pos_stride_d)
- *   lattice_values       [L, capacity, F]  contiguous (the reference parameter layout), F = nr_feat_per_level
+ *   lattice_values       [L, capacity, F]  contiguous (the reference parameter layout), F = nr_feat_per_level;
+ *                                          fp32, or fp16 when the configuration says so
  *   scale_factor         [L, pos_dim]      contiguous, from permuto_scale_factor()
  *   random_shift         [L, pos_dim]      contiguous
  *   anneal_window        [L]               contiguous
@@ -21,8 +22,20 @@
  *   lattice_grad         [L, capacity, F]  contiguous, the parameter's own layout
  *   positions_grad       [N, pos_dim]      contiguous
  *
+ * Alignment (checked; a violation returns PERMUTO_ERR_INVALID_ARGUMENT):
+ *   lattice_values                          4*F bytes (2*F for an fp16 table): all features of a slot
+ *                                           move in one access
+ *   features, grad_features, lattice_grad,
+ *   grad_grad_features                      8 bytes for F = 2, 16 bytes for F = 4 and 8
+ *   32-byte alignment of the feature / gradient rows (base pointer and W*4 a multiple of 32)
+ *   is not required but selects the fast path that moves 8 floats of a row per access; offset
+ *   views that break it fall back to per-level accesses with identical results.
+ *   positions: 4 bytes; contiguous rows on a base aligned to pos_dim*4 bytes are read with one
+ *   vector load when pos_dim is 2 or 4.
+ *
  * Every function returns PERMUTO_OK or a negative status; permuto_last_error() gives the
- * message of the last failure on the calling thread.  Nothing throws or aborts.
+ * message of the last failure on the calling thread (every failing entry point sets it, the
+ * measurement aid included).  Nothing throws or aborts.
  */
 #ifndef PERMUTO_B200_H
 #define PERMUTO_B200_H
@@ -33,7 +46,7 @@
 extern "C" {
 #endif
 
-#define PERMUTO_ABI_VERSION 1
+#define PERMUTO_ABI_VERSION 2
 
 enum {
     PERMUTO_OK = 0,
@@ -56,7 +69,13 @@ typedef struct permuto_config {
     int32_t levels_per_pass;   /* scheduling hint: levels one sweep over the points handles, a
                                   multiple of 8/F; 0 = chosen from the capacity (no reference
                                   counterpart; results do not depend on it)                    */
+    int32_t table_dtype;       /* storage type of lattice_values: PERMUTO_TABLE_F32 (the reference's)
+                                  or PERMUTO_TABLE_F16 (storage only: arithmetic, outputs and every
+                                  gradient stay fp32; the reference only hints at a half-precision
+                                  table, kernels/permutohedral_encoding/EncodingGPU.cuh:12)     */
 } permuto_config;
+
+enum { PERMUTO_TABLE_F32 = 0, PERMUTO_TABLE_F16 = 1 };
 
 /* Per-call lattice inputs shared by every entry point.  Replaces the reference's
  * EncodingInput (Encoding.cuh:14-29) plus the scale/shift tensors of EncodingFixedParams. */
@@ -65,7 +84,7 @@ typedef struct permuto_inputs {
     const float *positions;
     int64_t pos_stride_n;
     int64_t pos_stride_d;
-    const float *lattice_values;
+    const void *lattice_values; /* float, or __half when cfg->table_dtype == PERMUTO_TABLE_F16 */
     const float *scale_factor;
     const float *random_shift;
     const float *anneal_window;
@@ -120,6 +139,24 @@ int permuto_double_backward(const permuto_config *cfg, const permuto_inputs *in,
  *   bary  fp32  [N, L, pos_dim+1]            rank  int32 [N, L, pos_dim+1] */
 int permuto_debug_lattice(const permuto_config *cfg, const permuto_inputs *in, int32_t *keys,
                           int32_t *slots, float *bary, int32_t *rank, void *stream);
+
+/* Flags of permuto_adam_step. */
+enum {
+    PERMUTO_ADAM_SKIP_UNTOUCHED = 1, /* leave entries alone whose gradient and both moments are zero (exact when
+                                        weight_decay == 0; ignored otherwise)                                    */
+    PERMUTO_ADAM_ZERO_GRAD = 2       /* clear the gradient in the same pass (the next backward then accumulates
+                                        without PERMUTO_ZERO_OUTPUTS)                                            */
+};
+
+/* One AdamW step (amsgrad off) over n fp32 elements -- the lattice values, their gradient and the two
+ * moment arrays, all [L, capacity, F] contiguous and 16-byte aligned -- in a single kernel.  Replaces the
+ * optimizer the reference's training loops run over the table (examples/performance.py:161,101:
+ * torch.optim.AdamW(betas=(0.9, 0.99), eps=1e-15, weight_decay=0); examples/train_toy_example.py:30) and
+ * follows torch's update order (hyper-parameters are doubles, combined in double and rounded to fp32
+ * once, as torch does with Python scalars); `step` counts from 1.  The moments start as zeros (caller-allocated). */
+int permuto_adam_step(float *values, float *grad, float *exp_avg, float *exp_avg_sq, int64_t n, double lr,
+                      double beta1, double beta2, double eps, double weight_decay, int64_t step,
+                      uint32_t flags, void *stream);
 
 /* Measurement aid with no counterpart in the reference: launches, from every SM at full
  * occupancy, `accesses_per_thread` (a multiple of 4) independent random accesses per thread over

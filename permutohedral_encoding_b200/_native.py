@@ -21,28 +21,33 @@ import numpy as np
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-# PERMUTO_B200_LIB points at another build of the same library (e.g. one made with other tuning macros)
+# PERMUTO_B200_LIB names another build of the same library (`python -m permutohedral_encoding_b200.build --out ...`)
 LIB_PATH = os.environ.get("PERMUTO_B200_LIB") or os.path.join(_PKG_DIR, "libpermuto_b200.so")
 
+ABI_VERSION = 2
 PERMUTO_OK = 0
+PERMUTO_TABLE_F32 = 0
+PERMUTO_TABLE_F16 = 1
 PERMUTO_ERR_INVALID_ARGUMENT = -1
 PERMUTO_ERR_UNSUPPORTED = -2
 PERMUTO_ERR_CUDA = -3
 PERMUTO_ZERO_OUTPUTS = 1
 PERMUTO_NO_AGGREGATE = 2
 PERMUTO_KEEP_POSITIONS_GRAD = 4
+PERMUTO_ADAM_SKIP_UNTOUCHED = 1
+PERMUTO_ADAM_ZERO_GRAD = 2
 
 EXPORTED_SYMBOLS = (
     "permuto_abi_version", "permuto_last_error", "permuto_extra_levels", "permuto_scale_factor",
     "permuto_forward", "permuto_backward", "permuto_double_backward", "permuto_debug_lattice",
-    "permuto_probe_random_access",
+    "permuto_probe_random_access", "permuto_adam_step",
 )
 
 
 class PermutoConfig(C.Structure):
     _fields_ = [("pos_dim", C.c_int32), ("nr_feat_per_level", C.c_int32), ("nr_levels", C.c_int32),
                 ("capacity", C.c_int32), ("concat_points", C.c_int32), ("points_scaling", C.c_float),
-                ("levels_per_pass", C.c_int32)]
+                ("levels_per_pass", C.c_int32), ("table_dtype", C.c_int32)]
 
 
 class PermutoInputs(C.Structure):
@@ -78,8 +83,11 @@ def _load() -> C.CDLL:
     lib.permuto_probe_random_access.restype = C.c_int
     lib.permuto_probe_random_access.argtypes = [C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.POINTER(C.c_int64),
                                                 C.c_void_p]
-    if lib.permuto_abi_version() != 1:
-        raise ImportError(f"{LIB_PATH}: ABI version {lib.permuto_abi_version()} != 1; rebuild the extension")
+    lib.permuto_adam_step.restype = C.c_int
+    lib.permuto_adam_step.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_double, C.c_double,
+                                      C.c_double, C.c_double, C.c_double, C.c_int64, C.c_uint32, C.c_void_p]
+    if lib.permuto_abi_version() != ABI_VERSION:
+        raise ImportError(f"{LIB_PATH}: ABI version {lib.permuto_abi_version()} != {ABI_VERSION}; rebuild the extension")
     return lib
 
 
@@ -146,8 +154,11 @@ class EncodingInput:
     """Per-call bundle (reference: include/permutohedral_encoding/Encoding.cuh:14-29)."""
 
     def __init__(self, lattice_values, positions, anneal_window, require_lattice_values_grad,
-                 require_positions_grad):
+                 require_positions_grad, lattice_values_half=None):
         self.m_lattice_values = lattice_values
+        # optional fp16 copy of the values that the kernels gather from instead (storage only:
+        # arithmetic and gradients stay fp32); no counterpart in the reference
+        self.m_lattice_values_half = lattice_values_half
         self.m_positions_raw = positions
         self.m_anneal_window = anneal_window
         self.m_require_lattice_values_grad = bool(require_lattice_values_grad)
@@ -176,8 +187,7 @@ class EncodingFixedParams:
             raise RuntimeError("Encoding: pos_dim must be 2,3,4,5,6 or 7")
         self.m_scale_factor_host = torch.from_numpy(scale_factor(self.m_sigmas_list, self.m_pos_dim))
         self._scale_by_device = {}
-        # scheduling hint of the kernels (0 = automatic); PERMUTO_LEVELS_PER_PASS overrides it for experiments
-        self.levels_per_pass = int(os.environ.get("PERMUTO_LEVELS_PER_PASS", "0"))
+        self.levels_per_pass = 0  # scheduling hint of the kernels (0 = automatic; results never depend on it)
 
     def scale_factor_on(self, device) -> torch.Tensor:
         device = torch.device(device)
@@ -187,12 +197,14 @@ class EncodingFixedParams:
             self._scale_by_device[device] = t
         return t
 
-    def config(self) -> PermutoConfig:
-        cached = self.__dict__.get("_cfg")
+    def config(self, table_half: bool = False) -> PermutoConfig:
+        key = "_cfg_f16" if table_half else "_cfg_f32"
+        cached = self.__dict__.get(key)
         if cached is None or cached.levels_per_pass != int(self.levels_per_pass):
             cached = PermutoConfig(self.m_pos_dim, self.m_nr_feat_per_level, self.m_nr_levels, self.m_capacity,
-                                   int(self.m_concat_points), self.m_points_scaling, int(self.levels_per_pass))
-            self._cfg = cached
+                                   int(self.m_concat_points), self.m_points_scaling, int(self.levels_per_pass),
+                                   PERMUTO_TABLE_F16 if table_half else PERMUTO_TABLE_F32)
+            self.__dict__[key] = cached
         return cached
 
 
@@ -206,6 +218,8 @@ class EncodingWrapper:
             raise RuntimeError("Encoding: nr_feat_per_level must be 2, 4 or 8")
         self.fixed = fixed_params
         self.aggregate_collisions = True
+        self.backward_hook = None          # set by distributed.LatticeGradAllReduce
+        self.double_backward_hook = None
         self._feat = int(nr_feat_per_level)
         self._width = self._feat * (fixed_params.m_nr_levels + extra_levels(
             fixed_params.m_pos_dim, fixed_params.m_concat_points, self._feat))
@@ -234,8 +248,13 @@ class EncodingWrapper:
         if not lv.is_contiguous():
             raise RuntimeError("We assume that the lattice_values_monolithic are contiguous because in the cuda "
                                "code we make a load of 2 float values at a time")
-        if lv.dtype != torch.float32 or lv.device != pos.device:
-            raise RuntimeError("lattice_values should be float32 on the device of the positions")
+        if lv.dtype not in (torch.float32, torch.float16) or lv.device != pos.device:
+            raise RuntimeError("lattice_values should be float32 (or float16 storage) on the device of the positions")
+        half = inp.m_lattice_values_half
+        if half is not None and (half.dtype != torch.float16 or half.shape != lv.shape or half.device != lv.device
+                                 or not half.is_contiguous()):
+            raise RuntimeError("lattice_values_half should be a contiguous float16 tensor of the shape and device "
+                               "of lattice_values")
         if tuple(shift.shape) != (fp.m_nr_levels, fp.m_pos_dim):
             raise RuntimeError("Random shift should be nr of resolutions x pos dim")
         if aw.dim() != 1 or aw.shape[0] != fp.m_nr_levels:
@@ -252,10 +271,19 @@ class EncodingWrapper:
         if aw.device != dev or aw.dtype != torch.float32 or not aw.is_contiguous():
             aw = aw.detach().to(device=dev, dtype=torch.float32).contiguous()
         scale = fp.scale_factor_on(dev)
-        keep = (shift, aw, scale)
+        table = self._table(inp)
+        keep = (shift, aw, scale, table)
         ins = PermutoInputs(pos.shape[0], pos.data_ptr(), pos.stride(0), pos.stride(1),
-                            inp.m_lattice_values.data_ptr(), scale.data_ptr(), shift.data_ptr(), aw.data_ptr())
+                            table.data_ptr(), scale.data_ptr(), shift.data_ptr(), aw.data_ptr())
         return ins, keep
+
+    @staticmethod
+    def _table(inp: EncodingInput) -> torch.Tensor:
+        """The tensor the kernels gather from: the fp16 copy when one is attached."""
+        return inp.m_lattice_values_half if inp.m_lattice_values_half is not None else inp.m_lattice_values
+
+    def _config(self, inp: EncodingInput) -> PermutoConfig:
+        return self.fixed.config(self._table(inp).dtype == torch.float16)
 
     def output_width(self) -> int:
         return self._width
@@ -271,7 +299,7 @@ class EncodingWrapper:
         """features [N, 2*(L+extra)] (reference: Encoding<P,2>::forward + modules.py:87)."""
         self._check(inp)
         pos = inp.m_positions_raw
-        cfg = self.fixed.config()
+        cfg = self._config(inp)
         out = torch.empty((pos.shape[0], self.output_width()), dtype=torch.float32, device=pos.device)
         with _guard(pos.device):
             ins, keep = self._inputs(inp)
@@ -294,10 +322,11 @@ class EncodingWrapper:
                                f"expected {(n, self.output_width())}, got {tuple(grad_features.shape)}")
         if not grad_features.is_contiguous():
             raise RuntimeError("Grad sliced values needs to be contiguous. Please call .contiguous() on it")
-        cfg = fp.config()
+        cfg = self._config(inp)
         lv_grad = None
-        if inp.m_require_lattice_values_grad:
-            lv_grad = lattice_grad_out if lattice_grad_out is not None else torch.empty_like(inp.m_lattice_values)
+        if inp.m_require_lattice_values_grad:  # always fp32, whatever the storage type of the values
+            lv_grad = lattice_grad_out if lattice_grad_out is not None else \
+                torch.empty(inp.m_lattice_values.shape, dtype=torch.float32, device=pos.device)
         pos_grad = None
         flags = self._flags(zero)
         if inp.m_require_positions_grad:
@@ -330,8 +359,9 @@ class EncodingWrapper:
             raise RuntimeError("The nr of positions should match between the input positions and the sliced values")
         dpg = double_positions_grad.contiguous()
         gf = grad_features.contiguous()
-        cfg = fp.config()
-        lv_grad = torch.empty_like(inp.m_lattice_values) if need_lattice_grad else None
+        cfg = self._config(inp)
+        lv_grad = torch.empty(inp.m_lattice_values.shape, dtype=torch.float32, device=pos.device) \
+            if need_lattice_grad else None
         ggf = torch.empty_like(gf) if need_grad_grad_features else None
         with _guard(pos.device):
             ins, keep = self._inputs(inp)
@@ -350,7 +380,7 @@ class EncodingWrapper:
         slots = torch.empty((n, nl, d + 1), dtype=torch.int32, device=dev) if "slots" in want else None
         bary = torch.empty((n, nl, d + 1), dtype=torch.float32, device=dev) if "bary" in want else None
         rank = torch.empty((n, nl, d + 1), dtype=torch.int32, device=dev) if "rank" in want else None
-        cfg = fp.config()
+        cfg = self._config(inp)
         with _guard(dev):
             ins, keep = self._inputs(inp)
             check(lib.permuto_debug_lattice(C.byref(cfg), C.byref(ins), _ptr(keys), _ptr(slots), _ptr(bary),

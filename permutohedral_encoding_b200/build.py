@@ -27,7 +27,7 @@ def _nvcc() -> str:
 
 
 def _sources():
-    names = ["permuto_dim.cu", "permuto_cabi.cu", "permuto_probe.cu", "permuto_geometry.cuh",
+    names = ["permuto_dim.cu", "permuto_cabi.cu", "permuto_probe.cu", "permuto_adam.cu", "permuto_geometry.cuh",
              "permuto_internal.h"]
     paths = [os.path.join(CSRC, n) for n in names if os.path.isfile(os.path.join(CSRC, n))]
     paths.append(os.path.join(INCLUDE, "permuto_b200.h"))
@@ -69,7 +69,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, 
     for d in DIMS:
         obj = os.path.join(OBJ_DIR, f"permuto_dim{d}.o")
         jobs.append(([_nvcc(), *flags, f"-DPERMUTO_DIM={d}", "-c", os.path.join(CSRC, "permuto_dim.cu"), "-o", obj], obj))
-    for name in ("permuto_cabi", "permuto_probe"):
+    for name in ("permuto_cabi", "permuto_probe", "permuto_adam"):
         src = os.path.join(CSRC, name + ".cu")
         if os.path.isfile(src):
             obj = os.path.join(OBJ_DIR, name + ".o")

@@ -10,10 +10,12 @@
 #include "permuto_internal.h"
 
 namespace {
-
 thread_local char g_error[512] = "";
+}
 
-int fail(int code, const char* fmt, ...) {
+namespace permuto {
+
+int set_error(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
@@ -21,8 +23,26 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+int sm_count() {
+    constexpr int kMaxDevices = 64;
+    static int cached[kMaxDevices] = {};  // 0 = not asked yet; racing writers store the same value
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMaxDevices && cached[dev] > 0) return cached[dev];
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMaxDevices) cached[dev] = sms;
+    return sms;
+}
+
+}  // namespace permuto
+
+namespace {
+
+using permuto::set_error;
+
 int cuda_fail(cudaError_t e, const char* what) {
-    return fail(PERMUTO_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return set_error(PERMUTO_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -32,25 +52,29 @@ int extra_levels(int pos_dim, int nr_feat, int concat) { return concat ? (pos_di
 // Checks shared by every entry point; the messages mirror the reference's CHECKs
 // (src/Encoding.cu:37-45, :63-66) and factory errors (Encoding.cuh:142,155).
 int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::Problem& p) {
-    if (!cfg || !in) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "cfg and in must not be NULL");
+    if (!cfg || !in) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "cfg and in must not be NULL");
     if (cfg->pos_dim < 2 || cfg->pos_dim > 7)
-        return fail(PERMUTO_ERR_UNSUPPORTED, "Encoding: pos_dim must be 2,3,4,5,6 or 7 (got %d)", cfg->pos_dim);
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "Encoding: pos_dim must be 2,3,4,5,6 or 7 (got %d)", cfg->pos_dim);
     if (cfg->nr_feat_per_level != 2 && cfg->nr_feat_per_level != 4 && cfg->nr_feat_per_level != 8)
-        return fail(PERMUTO_ERR_UNSUPPORTED, "Encoding: nr_feat_per_level must be 2, 4 or 8 (got %d)",
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "Encoding: nr_feat_per_level must be 2, 4 or 8 (got %d)",
                     cfg->nr_feat_per_level);
     if (cfg->nr_levels < 1 || cfg->nr_levels > 65535)
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "nr_levels must be in 1..65535 (got %d)", cfg->nr_levels);
-    if (cfg->capacity < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "capacity must be >= 1");
-    if (in->nr_positions < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "Why do we have 0 points");
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "nr_levels must be in 1..65535 (got %d)", cfg->nr_levels);
+    if (cfg->capacity < 1) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "capacity must be >= 1");
+    if (in->nr_positions < 1) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "Why do we have 0 points");
     if (in->nr_positions > (int64_t)0x7fffffff)
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "nr_positions must be below 2^31");
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "nr_positions must be below 2^31");
     if (!in->positions || !in->lattice_values || !in->scale_factor || !in->random_shift || !in->anneal_window)
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "positions, lattice_values, scale_factor, random_shift and "
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "positions, lattice_values, scale_factor, random_shift and "
                                                   "anneal_window must not be NULL");
     const int F = cfg->nr_feat_per_level;
-    if (!aligned(in->lattice_values, 4 * (size_t)F))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT,
-                    "lattice_values must be %d-byte aligned (all features of a slot are moved at once)", 4 * F);
+    if (cfg->table_dtype != PERMUTO_TABLE_F32 && cfg->table_dtype != PERMUTO_TABLE_F16)
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "table_dtype must be PERMUTO_TABLE_F32 or PERMUTO_TABLE_F16 (got %d)",
+                         cfg->table_dtype);
+    const int entry_bytes = (cfg->table_dtype == PERMUTO_TABLE_F16 ? 2 : 4) * F;
+    if (!aligned(in->lattice_values, (size_t)entry_bytes))
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT,
+                    "lattice_values must be %d-byte aligned (all features of a slot are moved at once)", entry_bytes);
     const int extra = extra_levels(cfg->pos_dim, F, cfg->concat_points);
     p.positions = in->positions;
     p.pos_stride_n = in->pos_stride_n;
@@ -64,12 +88,15 @@ int build_problem(const permuto_config* cfg, const permuto_inputs* in, permuto::
     p.capacity = (uint32_t)cfg->capacity;
     p.cap_is_pow2 = (cfg->capacity & (cfg->capacity - 1)) == 0;
     p.nr_feat = F;
+    p.table_half = cfg->table_dtype == PERMUTO_TABLE_F16 ? 1 : 0;
     p.width = F * (cfg->nr_levels + extra);
     p.level_begin = 0;
     p.level_end = cfg->nr_levels;
     p.extra_levels = extra;
     p.points_scaling = cfg->points_scaling;
     p.rows_vec8_ok = 0;
+    p.pos_vec_ok = (in->pos_stride_d == 1 && in->pos_stride_n == cfg->pos_dim &&
+                    aligned(in->positions, 4 * (size_t)cfg->pos_dim)) ? 1 : 0;
     p.levels_per_pass = cfg->levels_per_pass < 0 ? 0 : cfg->levels_per_pass;
     return PERMUTO_OK;
 }
@@ -110,10 +137,10 @@ int permuto_extra_levels(int32_t pos_dim, int32_t nr_feat_per_level, int32_t con
 }
 
 int permuto_scale_factor(const double* sigmas, int32_t nr_levels, int32_t pos_dim, float* out_host) {
-    if (!sigmas || !out_host) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "sigmas and out_host must not be NULL");
-    if (nr_levels < 1) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "nr_levels must be >= 1");
+    if (!sigmas || !out_host) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "sigmas and out_host must not be NULL");
+    if (nr_levels < 1) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "nr_levels must be >= 1");
     if (pos_dim < 2 || pos_dim > 7)
-        return fail(PERMUTO_ERR_UNSUPPORTED, "Encoding: pos_dim must be 2,3,4,5,6 or 7 (got %d)", pos_dim);
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "Encoding: pos_dim must be 2,3,4,5,6 or 7 (got %d)", pos_dim);
     for (int l = 0; l < nr_levels; ++l) {
         // the sigma list reaches the reference as std::vector<float>; its tensor-by-scalar
         // division multiplies the fp32 element by the fp32 reciprocal of the divisor
@@ -131,8 +158,8 @@ int permuto_scale_factor(const double* sigmas, int32_t nr_levels, int32_t pos_di
 int permuto_forward(const permuto_config* cfg, const permuto_inputs* in, float* features, void* stream) {
     permuto::ForwardArgs a;
     if (int rc = build_problem(cfg, in, a.p)) return rc;
-    if (!features) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "features must not be NULL");
-    if (!aligned(features, row_align(a.p))) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "features must be %d-byte aligned", (int)row_align(a.p));
+    if (!features) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "features must not be NULL");
+    if (!aligned(features, row_align(a.p))) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "features must be %d-byte aligned", (int)row_align(a.p));
     a.features = features;
     a.p.rows_vec8_ok = rows_vec8(a.p, features, nullptr);
     cudaError_t err;
@@ -147,13 +174,13 @@ int permuto_backward(const permuto_config* cfg, const permuto_inputs* in, const 
                      uint32_t flags, void* stream) {
     permuto::BackwardArgs a;
     if (int rc = build_problem(cfg, in, a.p)) return rc;
-    if (!grad_features) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must not be NULL");
+    if (!grad_features) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must not be NULL");
     if (!aligned(grad_features, row_align(a.p)))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be %d-byte aligned", (int)row_align(a.p));
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be %d-byte aligned", (int)row_align(a.p));
     if (lattice_grad && !aligned(lattice_grad, row_align(a.p)))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be %d-byte aligned", (int)row_align(a.p));
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be %d-byte aligned", (int)row_align(a.p));
     if (level_begin < 0 || level_end > cfg->nr_levels || level_begin > level_end)
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "level range [%d, %d) outside [0, %d)", level_begin, level_end,
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "level range [%d, %d) outside [0, %d)", level_begin, level_end,
                     cfg->nr_levels);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     a.p.level_begin = level_begin;
@@ -184,15 +211,15 @@ int permuto_double_backward(const permuto_config* cfg, const permuto_inputs* in,
                             uint32_t flags, void* stream) {
     permuto::DoubleBackwardArgs a;
     if (int rc = build_problem(cfg, in, a.p)) return rc;
-    if (!double_positions_grad) return fail(PERMUTO_ERR_INVALID_ARGUMENT, "double_positions_grad must not be NULL");
+    if (!double_positions_grad) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "double_positions_grad must not be NULL");
     if (lattice_grad && !grad_features)
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features is needed for the lattice gradient");
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features is needed for the lattice gradient");
     if (grad_features && !aligned(grad_features, row_align(a.p)))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be %d-byte aligned", (int)row_align(a.p));
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "grad_features must be %d-byte aligned", (int)row_align(a.p));
     if (lattice_grad && !aligned(lattice_grad, row_align(a.p)))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be %d-byte aligned", (int)row_align(a.p));
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "lattice_grad must be %d-byte aligned", (int)row_align(a.p));
     if (grad_grad_features && !aligned(grad_grad_features, row_align(a.p)))
-        return fail(PERMUTO_ERR_INVALID_ARGUMENT, "grad_grad_features must be %d-byte aligned", (int)row_align(a.p));
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "grad_grad_features must be %d-byte aligned", (int)row_align(a.p));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     a.double_positions_grad = double_positions_grad;
     a.grad_features = grad_features;

@@ -16,6 +16,8 @@
 //   forward_kernel          kernels/permutohedral_encoding/EncodingGPU.cuh:68-256
 //   backward_kernel         EncodingGPU.cuh:259-414 (table) and :530-769 (positions), fused
 //   double_backward_kernel  EncodingGPU.cuh:1016-1257 and :1260-1493, fused
+#include <cuda_fp16.h>
+
 #include "permuto_geometry.cuh"
 #include "permuto_internal.h"
 
@@ -53,7 +55,25 @@ constexpr int min_blocks(int feats, bool gather_only) {
 }
 constexpr unsigned kFullMask = 0xffffffffu;
 
+// A point's coordinates.  Rows of 2 or 4 contiguous floats on an aligned base are one 8- or
+// 16-byte load (consecutive threads then read consecutive vectors); every other case -- odd
+// pos_dim, strided or transposed positions -- takes one 4-byte load per coordinate, which for
+// contiguous rows still touches each 128-byte line from a single warp instruction group.
 __device__ __forceinline__ void load_pos(const Problem& p, int64_t n, float (&pos)[D]) {
+    if ((D == 2 || D == 4) && p.pos_vec_ok) {
+        if (D == 2) {
+            const float2 t = __ldg(reinterpret_cast<const float2*>(p.positions) + n);
+            pos[0] = t.x;
+            pos[D - 1] = t.y;
+        } else {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(p.positions) + n);
+            pos[0] = t.x;
+            pos[1 % D] = t.y;
+            pos[2 % D] = t.z;
+            pos[3 % D] = t.w;
+        }
+        return;
+    }
     const float* src = p.positions + n * p.pos_stride_n;
 #pragma unroll
     for (int i = 0; i < D; ++i) pos[i] = __ldg(src + i * p.pos_stride_d);
@@ -111,16 +131,50 @@ __device__ __forceinline__ void store8(float* dst, const float (&v)[8]) {
                  : "memory");
 }
 
-// aligned gather of one table entry (all F features) through the read-only path
-template <int F>
-__device__ __forceinline__ void gather(const float* __restrict__ level_base, uint32_t slot, float (&v)[F]) {
-    const float* src = level_base + (size_t)slot * F;
-    if (F == 8) {
-        asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
-                     : "l"(src));
+// Aligned gather of one table entry (all F features) through the read-only path.  HALF: the
+// table is stored as fp16 (storage only -- every product and sum below stays fp32), so an entry is
+// 2F bytes: one 4-, 8- or 16-byte load.  Random accesses are bound by operations per second, not
+// bytes, so a 4-feature fp16 entry (8 bytes) costs what a 2-feature fp32 entry costs, and the
+// table takes half the room in L2.
+template <int F, bool HALF>
+__device__ __forceinline__ void gather(const void* __restrict__ table, int level, uint32_t capacity, uint32_t slot,
+                                       float (&v)[F]) {
+    const size_t entry = (size_t)level * capacity + slot;
+    if (HALF) {
+        const __half2* src = reinterpret_cast<const __half2*>(table) + entry * (F / 2);
+        if (F == 2) {
+            const unsigned raw = __ldg(reinterpret_cast<const unsigned*>(src));
+            const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&raw));
+            v[0] = t.x;
+            v[1] = t.y;
+        } else if (F == 4) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src));
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            v[0] = a.x;
+            v[1] = a.y;
+            v[2 % F] = b.x;
+            v[3 % F] = b.y;
+        } else {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+            const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[q]));
+                v[(2 * q) % F] = t.x;
+                v[(2 * q + 1) % F] = t.y;
+            }
+        }
     } else {
-        load_feats<F>(src, v);
+        const float* src = reinterpret_cast<const float*>(table) + entry * F;
+        if (F == 8) {
+            asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=f"(v[0]), "=f"(v[1]), "=f"(v[2 % F]), "=f"(v[3 % F]), "=f"(v[4 % F]), "=f"(v[5 % F]),
+                           "=f"(v[6 % F]), "=f"(v[7 % F])
+                         : "l"(src));
+        } else {
+            load_feats<F>(src, v);
+        }
     }
 }
 
@@ -182,7 +236,7 @@ __device__ __forceinline__ void store_row_segment(const Problem& p, float* rows,
 // ------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------
-template <int F, int LPS>
+template <int F, int LPS, bool HALF>
 __global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD : min_blocks(F, false))) forward_kernel(const ForwardArgs a) {
     const Problem& p = a.p;
     const int64_t n = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -209,10 +263,9 @@ __global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD
                     locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
                     uint32_t slot[D + 1];
                     to_slots(p, s, slot);
-                    const float* base = p.table + (size_t)l * p.capacity * F;
                     float v[D + 1][F];
 #pragma unroll
-                    for (int r = 0; r <= D; ++r) gather<F>(base, slot[r], v[r]);
+                    for (int r = 0; r <= D; ++r) gather<F, HALF>(p.table, l, p.capacity, slot[r], v[r]);
 #pragma unroll
                     for (int r = 0; r <= D; ++r) {
                         const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:234
@@ -248,59 +301,112 @@ __global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD
 // lanes (log2 of the largest group rounds) leaves the group total in its lowest lane, and only
 // that lane issues the vector reduction.  The summation order is fixed by the lane order, so a
 // warp's contribution is deterministic.
-template <int F>
-__device__ __forceinline__ void merge_and_red(float* level_base, uint32_t slot, float (&x)[F], bool active,
-                                              unsigned lane, unsigned group) {
-    const int largest = __reduce_max_sync(kFullMask, __popc(group));
-    const unsigned above = group & (0xfffffffeu << lane);
-    int next = above ? (__ffs(above) - 1) : -1;
-    for (int span = 1; span < largest; span <<= 1) {  // warp-uniform trip count
-        const int src = next >= 0 ? next : (int)lane;
-        float x2[F];
-#pragma unroll
-        for (int f = 0; f < F; ++f) x2[f] = __shfl_sync(kFullMask, x[f], src);
-        const int n2 = __shfl_sync(kFullMask, next, src);
-        if (next >= 0) {
-#pragma unroll
-            for (int f = 0; f < F; ++f) x[f] += x2[f];
-            next = n2;
-        }
-    }
-    const bool leader = (group & ((1u << lane) - 1u)) == 0u;
-    if (leader && active) red_add<F>(level_base, slot, x);
-}
-
+//
+// The d+1 vertices are merged together, round by round, not one after the other: a round is a
+// chain match/shuffle -> add -> shuffle whose latency nothing else in the warp can hide, and the
+// d+1 chains are independent of each other.  (With the vertices merged one after the other the
+// coarse half of the levels took as long as the fine half, although it sends a quarter of the
+// reductions to L2.)
+//
 // Merging pays only while a warp's 32 points share slots: per warp and vertex the number of
 // distinct slots on the training shape is 6, 7, 9, 15, 22, 38, 63, 96, 116, 124 of 128 for levels
 // 0..9 and 128 from level 11 on, and match.any itself is slowest when all keys differ.  The
 // match of vertex 0 doubles as the probe: when it finds more than kMergeBelow distinct slots the
 // level is scattered directly and -- collisions only get rarer towards finer levels -- the warp
-// stops probing for the rest of its pass (`probe` is warp-uniform state owned by the caller).
+// stops probing until its walk over the levels restarts at the coarsest one.
+//
+// Blocks start their walk over the steps of a pass at different steps (block index modulo the
+// number of steps), so that at any moment the blocks in flight work on different levels instead
+// of all sending their reductions to the few hot slots of the same coarse level (2-4 % on the
+// scatter kernels).
 #ifndef PERMUTO_MERGE_BELOW
 #define PERMUTO_MERGE_BELOW 24
 #endif
+#ifndef PERMUTO_STAGGER
+#define PERMUTO_STAGGER 1
+#endif
 constexpr int kMergeBelow = PERMUTO_MERGE_BELOW;
+constexpr bool kStagger = PERMUTO_STAGGER != 0;
+
+// per-thread state of the scatter of one warp
+struct Scatter {
+    unsigned lane;
+    bool active;  // this lane owns a point
+    bool probe;   // warp-uniform: keep testing levels for mergeable collisions
+};
+
+// Vertices merged side by side: all of them up to pos_dim 4; beyond that half at a time, which
+// keeps the d+1 partial sums, group masks and chain pointers within the register budget.
+#ifndef PERMUTO_MERGE_CHUNK
+#define PERMUTO_MERGE_CHUNK (PERMUTO_DIM <= 4 ? PERMUTO_DIM + 1 : (PERMUTO_DIM + 2) / 2)
+#endif
+constexpr int kMergeChunk = PERMUTO_MERGE_CHUNK;
+
+// vertices [R0, R0 + CNT) of one level: segmented suffix sums over the lanes of every group,
+// then one reduction per group from its lowest lane.  group[0] is passed in when R0 == 0.
+template <int F, int R0, int CNT>
+__device__ __forceinline__ void merge_vertices(const Scatter& sc, float* level_base, const uint32_t (&slot)[D + 1],
+                                               float (&add)[D + 1][F], unsigned group0) {
+    const unsigned lane = sc.lane;
+    const uint32_t idle = 0xffffffffu - lane;  // idle lanes match nobody
+    const unsigned below = (1u << lane) - 1u;
+    unsigned group[CNT];
+    int next[CNT];  // next higher lane of the same group, -1 at the end of the chain
+    int largest = 0;
+#pragma unroll
+    for (int c = 0; c < CNT; ++c) {
+        group[c] = (R0 == 0 && c == 0) ? group0 : __match_any_sync(kFullMask, sc.active ? slot[R0 + c] : idle);
+        largest = max(largest, __popc(group[c]));
+        const unsigned above = group[c] & (0xfffffffeu << lane);
+        next[c] = above ? (__ffs(above) - 1) : -1;
+    }
+    largest = __reduce_max_sync(kFullMask, largest);
+    for (int span = 1; span < largest; span <<= 1) {  // warp-uniform trip count
+#pragma unroll
+        for (int c = 0; c < CNT; ++c) {
+            const int src = next[c] >= 0 ? next[c] : (int)lane;
+            float x2[F];
+#pragma unroll
+            for (int f = 0; f < F; ++f) x2[f] = __shfl_sync(kFullMask, add[R0 + c][f], src);
+            const int n2 = __shfl_sync(kFullMask, next[c], src);
+            if (next[c] >= 0) {
+#pragma unroll
+                for (int f = 0; f < F; ++f) add[R0 + c][f] += x2[f];
+                next[c] = n2;
+            }
+        }
+    }
+    if (sc.active) {
+#pragma unroll
+        for (int c = 0; c < CNT; ++c)
+            if ((group[c] & below) == 0u) red_add<F>(level_base, slot[R0 + c], add[R0 + c]);
+    }
+}
+
+template <int F, int R0>
+__device__ __forceinline__ void merge_from(const Scatter& sc, float* level_base, const uint32_t (&slot)[D + 1],
+                                           float (&add)[D + 1][F], unsigned group0) {
+    if constexpr (R0 <= D) {
+        constexpr int CNT = (D + 1 - R0) < kMergeChunk ? (D + 1 - R0) : kMergeChunk;
+        merge_vertices<F, R0, CNT>(sc, level_base, slot, add, group0);
+        merge_from<F, R0 + CNT>(sc, level_base, slot, add, group0);
+    }
+}
 
 template <int F>
-__device__ __forceinline__ void scatter_level(float* level_base, const uint32_t (&slot)[D + 1], float (&add)[D + 1][F],
-                                              bool active, unsigned lane, bool& probe) {
-    if (probe) {
-        const uint32_t idle = 0xffffffffu - lane;  // idle lanes match nobody
-        const unsigned group0 = __match_any_sync(kFullMask, active ? slot[0] : idle);
-        const bool leader0 = (group0 & ((1u << lane) - 1u)) == 0u;
-        const int distinct = __popc(__ballot_sync(kFullMask, leader0));
+__device__ __forceinline__ void scatter_level(Scatter& sc, float* level_base, const uint32_t (&slot)[D + 1],
+                                              float (&add)[D + 1][F]) {
+    if (sc.probe) {
+        const unsigned lane = sc.lane;
+        const unsigned group0 = __match_any_sync(kFullMask, sc.active ? slot[0] : 0xffffffffu - lane);
+        const int distinct = __popc(__ballot_sync(kFullMask, (group0 & ((1u << lane) - 1u)) == 0u));
         if (distinct <= kMergeBelow) {
-            merge_and_red<F>(level_base, slot[0], add[0], active, lane, group0);
-#pragma unroll
-            for (int r = 1; r <= D; ++r) {
-                const unsigned group = __match_any_sync(kFullMask, active ? slot[r] : idle);
-                merge_and_red<F>(level_base, slot[r], add[r], active, lane, group);
-            }
+            merge_from<F, 0>(sc, level_base, slot, add, group0);
             return;
         }
-        probe = false;
+        sc.probe = false;
     }
-    if (active) {
+    if (sc.active) {
 #pragma unroll
         for (int r = 0; r <= D; ++r) red_add<F>(level_base, slot[r], add[r]);
     }
@@ -309,7 +415,7 @@ __device__ __forceinline__ void scatter_level(float* level_base, const uint32_t 
 // ------------------------------------------------------------------------------------------
 // first-order backward: table gradient (scatter) and/or position gradient (gather)
 // ------------------------------------------------------------------------------------------
-template <int F, int LPS, bool TABLE, bool POS>
+template <int F, int LPS, bool TABLE, bool POS, bool HALF>
 __global__ void __launch_bounds__(kThreads, min_blocks(F, !TABLE))
 backward_kernel(const BackwardArgs a) {
     const Problem& p = a.p;
@@ -327,17 +433,24 @@ backward_kernel(const BackwardArgs a) {
     float dpos[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) dpos[i] = 0.f;
-    bool probe = a.aggregate != 0;
+    Scatter sc{lane, active, a.aggregate != 0};
+
+    // steps of the pass are walked cyclically from a block-dependent start (see PERMUTO_STAGGER)
+    const int nsteps = (pass_end - pass_begin + LPS - 1) / LPS;
+    int step = (TABLE && kStagger) ? (int)(blockIdx.x % (unsigned)nsteps) : 0;
 
     // the next step's 32 bytes of the gradient row are requested before this step is worked on
     float g_next[F * LPS];
-    load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin, g_next);
+    load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin + step * LPS, g_next);
 #pragma unroll 1
-    for (int l0 = pass_begin; l0 < pass_end; l0 += LPS) {
+    for (int it = 0; it < nsteps; ++it) {
+        const int l0 = pass_begin + step * LPS;
+        step = (step + 1 == nsteps) ? 0 : step + 1;
+        if (TABLE && l0 == pass_begin) sc.probe = a.aggregate != 0;
         float g[F * LPS];
 #pragma unroll
         for (int i = 0; i < F * LPS; ++i) g[i] = g_next[i];
-        if (l0 + LPS < pass_end) load_row_segment<F, LPS>(p, a.grad_features, n, l0 + LPS, g_next);
+        if (it + 1 < nsteps) load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin + step * LPS, g_next);
 #pragma unroll
         for (int k = 0; k < LPS; ++k) {
             const int l = l0 + k;
@@ -351,7 +464,6 @@ backward_kernel(const BackwardArgs a) {
 
             if (POS) {
                 // EncodingGPU.cuh:671-749
-                const float* base = p.table + (size_t)l * p.capacity * F;
                 float gs[F];  // upstream gradient with the level weight and 1/(d+1) folded in
 #pragma unroll
                 for (int f = 0; f < F; ++f) gs[f] = g[F * k + f] * w_lvl * kInv;
@@ -359,7 +471,7 @@ backward_kernel(const BackwardArgs a) {
 #pragma unroll
                 for (int r = 0; r <= D; ++r) {
                     float v[F];
-                    gather<F>(base, slot[r], v);
+                    gather<F, HALF>(p.table, l, p.capacity, slot[r], v);
                     float t = v[0] * gs[0];
 #pragma unroll
                     for (int f = 1; f < F; ++f) t = fmaf(v[f], gs[f], t);
@@ -397,7 +509,7 @@ backward_kernel(const BackwardArgs a) {
 #pragma unroll
                     for (int f = 0; f < F; ++f) add[r][f] = s.bary[r] * gw[f];
                 }
-                scatter_level<F>(gbase, slot, add, active, lane, probe);
+                scatter_level<F>(sc, gbase, slot, add);
             }
         }
     }
@@ -411,7 +523,7 @@ backward_kernel(const BackwardArgs a) {
 // ------------------------------------------------------------------------------------------
 // double backward of the position gradient
 // ------------------------------------------------------------------------------------------
-template <int F, int LPS, bool TABLE, bool GGF>
+template <int F, int LPS, bool TABLE, bool GGF, bool HALF>
 __global__ void __launch_bounds__(kThreads, min_blocks(F, false)) double_backward_kernel(const DoubleBackwardArgs a) {
     const Problem& p = a.p;
     const int64_t n_raw = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -426,17 +538,22 @@ __global__ void __launch_bounds__(kThreads, min_blocks(F, false)) double_backwar
     load_pos(p, n, pos);
 #pragma unroll
     for (int i = 0; i < D; ++i) dpg[i] = __ldg(a.double_positions_grad + n * D + i);
-    bool probe = a.aggregate != 0;  // as in backward_kernel
+    Scatter sc{lane, active, a.aggregate != 0};  // as in backward_kernel
+    const int nsteps = (pass_end - pass_begin + LPS - 1) / LPS;
+    int step = (TABLE && kStagger) ? (int)(blockIdx.x % (unsigned)nsteps) : 0;
 
     float g_next[F * LPS];  // as in backward_kernel: the next step's gradient segment is requested early
-    if (TABLE) load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin, g_next);
+    if (TABLE) load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin + step * LPS, g_next);
 #pragma unroll 1
-    for (int l0 = pass_begin; l0 < pass_end; l0 += LPS) {
+    for (int it = 0; it < nsteps; ++it) {
+        const int l0 = pass_begin + step * LPS;
+        step = (step + 1 == nsteps) ? 0 : step + 1;
+        if (TABLE && l0 == pass_begin) sc.probe = a.aggregate != 0;
         float g[F * LPS];
         if (TABLE) {
 #pragma unroll
             for (int i = 0; i < F * LPS; ++i) g[i] = g_next[i];
-            if (l0 + LPS < pass_end) load_row_segment<F, LPS>(p, a.grad_features, n, l0 + LPS, g_next);
+            if (it + 1 < nsteps) load_row_segment<F, LPS>(p, a.grad_features, n, pass_begin + step * LPS, g_next);
         }
         float out[F * LPS];
 #pragma unroll
@@ -481,11 +598,10 @@ __global__ void __launch_bounds__(kThreads, min_blocks(F, false)) double_backwar
                     dBw[0] = (sdE[D] - sdE[0]) * w_lvl;
 
                     if (GGF) {
-                        const float* base = p.table + (size_t)l * p.capacity * F;
 #pragma unroll
                         for (int r = 0; r <= D; ++r) {
                             float v[F];
-                            gather<F>(base, slot[r], v);  // EncodingGPU.cuh:1484-1485
+                            gather<F, HALF>(p.table, l, p.capacity, slot[r], v);  // EncodingGPU.cuh:1484-1485
 #pragma unroll
                             for (int f = 0; f < F; ++f) o[f] = fmaf(dBw[r], v[f], o[f]);
                         }
@@ -498,7 +614,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(F, false)) double_backwar
 #pragma unroll
                             for (int f = 0; f < F; ++f) add[r][f] = dBw[r] * g[F * k + f];  // EncodingGPU.cuh:1244-1245
                         }
-                        scatter_level<F>(gbase, slot, add, active, lane, probe);
+                        scatter_level<F>(sc, gbase, slot, add);
                     }
                 }
             }
@@ -557,14 +673,14 @@ inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t, int 
     const int levels = p.level_end - p.level_begin;
     int lpp = requested;
     if (lpp <= 0) {
-        const double slice = 4.0 * p.nr_feat * p.capacity;
+        const double slice = (p.table_half ? 2.0 : 4.0) * p.nr_feat * p.capacity;
         const double mb = 1024.0 * 1024.0;
         if (t == Traffic::Scatter)
             lpp = levels;
         else if (t == Traffic::Gather)
             lpp = (int)(96.0 * mb / slice);
         else
-            lpp = (int)(64.0 * mb / (2.0 * slice));
+            lpp = (int)(64.0 * mb / (slice + 4.0 * p.nr_feat * p.capacity));  // values + their fp32 gradient
     }
     lpp = (lpp / lps) * lps;
     if (lpp < lps) lpp = lps;
@@ -583,7 +699,8 @@ inline bool use_single_level(const Problem& p) {
     const int lps = 8 / p.nr_feat;
     const int64_t steps = (p.level_end - p.level_begin + lps - 1) / lps;
     const int64_t blocks = ((p.n_points + kThreads - 1) / kThreads) * steps;
-    return lps > 1 && blocks < 2 * 148;
+    const int sms = sm_count();
+    return lps > 1 && blocks < 2 * (sms > 0 ? sms : 148);
 }
 
 template <class Args>
@@ -595,31 +712,44 @@ inline Args with_schedule(const Args& in, bool single, Traffic t) {
 
 template <int F, int LPS>
 cudaError_t launch_forward(const ForwardArgs& a, cudaStream_t st) {
-    forward_kernel<F, LPS><<<grid_for(a.p), kThreads, 0, st>>>(a);
+    if (a.p.table_half)
+        forward_kernel<F, LPS, true><<<grid_for(a.p), kThreads, 0, st>>>(a);
+    else
+        forward_kernel<F, LPS, false><<<grid_for(a.p), kThreads, 0, st>>>(a);
     return cudaGetLastError();
 }
 
+// The table is only read where something is gathered (position gradient, grad-grad features):
+// the scatter-only kernels have no fp16 variant.
 template <int F, int LPS>
 cudaError_t launch_backward(const BackwardArgs& a, cudaStream_t st) {
     const dim3 g = grid_for(a.p);
-    if (a.lattice_grad && a.positions_grad)
-        backward_kernel<F, LPS, true, true><<<g, kThreads, 0, st>>>(a);
-    else if (a.lattice_grad)
-        backward_kernel<F, LPS, true, false><<<g, kThreads, 0, st>>>(a);
-    else if (a.positions_grad)
-        backward_kernel<F, LPS, false, true><<<g, kThreads, 0, st>>>(a);
+    const bool h = a.p.table_half != 0;
+    if (a.lattice_grad && a.positions_grad) {
+        if (h) backward_kernel<F, LPS, true, true, true><<<g, kThreads, 0, st>>>(a);
+        else backward_kernel<F, LPS, true, true, false><<<g, kThreads, 0, st>>>(a);
+    } else if (a.lattice_grad) {
+        backward_kernel<F, LPS, true, false, false><<<g, kThreads, 0, st>>>(a);
+    } else if (a.positions_grad) {
+        if (h) backward_kernel<F, LPS, false, true, true><<<g, kThreads, 0, st>>>(a);
+        else backward_kernel<F, LPS, false, true, false><<<g, kThreads, 0, st>>>(a);
+    }
     return cudaGetLastError();
 }
 
 template <int F, int LPS>
 cudaError_t launch_double(const DoubleBackwardArgs& a, cudaStream_t st) {
     const dim3 g = grid_for(a.p);
-    if (a.lattice_grad && a.grad_grad_features)
-        double_backward_kernel<F, LPS, true, true><<<g, kThreads, 0, st>>>(a);
-    else if (a.lattice_grad)
-        double_backward_kernel<F, LPS, true, false><<<g, kThreads, 0, st>>>(a);
-    else if (a.grad_grad_features)
-        double_backward_kernel<F, LPS, false, true><<<g, kThreads, 0, st>>>(a);
+    const bool h = a.p.table_half != 0;
+    if (a.lattice_grad && a.grad_grad_features) {
+        if (h) double_backward_kernel<F, LPS, true, true, true><<<g, kThreads, 0, st>>>(a);
+        else double_backward_kernel<F, LPS, true, true, false><<<g, kThreads, 0, st>>>(a);
+    } else if (a.lattice_grad) {
+        double_backward_kernel<F, LPS, true, false, false><<<g, kThreads, 0, st>>>(a);
+    } else if (a.grad_grad_features) {
+        if (h) double_backward_kernel<F, LPS, false, true, true><<<g, kThreads, 0, st>>>(a);
+        else double_backward_kernel<F, LPS, false, true, false><<<g, kThreads, 0, st>>>(a);
+    }
     return cudaGetLastError();
 }
 

@@ -3,7 +3,9 @@
 //
 // Behaviour follows kernels/permutohedral_encoding/EncodingGPU.cuh:130-223 and :22-45 of the
 // reference (paths relative to its project root): the integer results (remainder-0 point,
-// ranks, keys, slots) are bit-identical to it, and the barycentric weights too.  The code is
+// ranks, keys, slots) are bit-identical to it; the barycentric weights agree to fp32 rounding
+// (about 1e-7 absolute) but not bit for bit, because nvcc contracts the reference's
+// `b[..] += (e - rem0) * inv` into fused multiply-adds in its own way.  The code is
 // organised differently: ranks are turned into a "sorted residual" vector with selects so
 // that nothing is indexed dynamically (no local memory), and the d+1 hashes are derived from
 // one base hash because the hash is linear over Z/2^32.

@@ -11,7 +11,7 @@ struct Problem {
     const float* positions;
     int64_t pos_stride_n;
     int64_t pos_stride_d;
-    const float* table;   // [L, C, F]
+    const void* table;    // [L, C, F], fp32 or (table_half) fp16
     const float* scale;   // [L, D]
     const float* shift;   // [L, D]
     const float* anneal;  // [L]
@@ -19,6 +19,7 @@ struct Problem {
     int32_t nr_levels;
     uint32_t capacity;
     int32_t cap_is_pow2;
+    int32_t table_half;   // the value table is stored as fp16 (gathers only; gradients stay fp32)
     int32_t nr_feat;      // F: features per level, 2, 4 or 8
     int32_t width;        // F * (L + extra): row length of features / gradients
     int32_t level_begin;  // levels [level_begin, level_end) are processed
@@ -26,6 +27,7 @@ struct Problem {
     int32_t extra_levels; // concat rows
     float points_scaling;
     int32_t rows_vec8_ok; // feature rows may be moved with 32-byte vector accesses
+    int32_t pos_vec_ok;   // positions are contiguous rows on a base aligned to the row size (pos_dim 2, 4)
     int32_t levels_per_pass; // in: requested (0 = automatic); set by the launcher for the kernel
 };
 
@@ -58,6 +60,13 @@ struct DebugArgs {
     float* bary;
     int32_t* rank;
 };
+
+// Records the message permuto_last_error() returns on this thread and hands back `code`;
+// every failing entry point goes through it (defined in permuto_cabi.cu).
+int set_error(int code, const char* fmt, ...);
+
+// Number of multiprocessors of the current device (cached per device); 0 if the query fails.
+int sm_count();
 
 // Defined once per pos_dim in permuto_dim.cu (compiled with -DPERMUTO_DIM=d).
 #define PERMUTO_DECLARE_DIM(d)                                                        \

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include "permuto_b200.h"
+#include "permuto_internal.h"
 
 namespace {
 
@@ -61,13 +62,19 @@ __global__ void __launch_bounds__(256) probe_kernel(float* region, uint32_t entr
 
 extern "C" int permuto_probe_random_access(int32_t kind, float* region, int64_t region_bytes, int32_t accesses_per_thread,
                                            int64_t* total_accesses, void* stream) {
-    if (!region || kind < 0 || kind > 3 || accesses_per_thread < 4 || (accesses_per_thread & 3)) return PERMUTO_ERR_INVALID_ARGUMENT;
+    using permuto::set_error;
+    if (!region || kind < 0 || kind > 3)
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "probe: region must not be NULL and kind must be 0..3 (got %d)", kind);
+    if (accesses_per_thread < 4 || (accesses_per_thread & 3))
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "probe: accesses_per_thread must be a positive multiple of 4 (got %d)",
+                         accesses_per_thread);
     const int entry_bytes = (kind == 0 || kind == 2) ? 8 : 16;
-    if (region_bytes < entry_bytes || region_bytes / entry_bytes > 0x7fffffffLL) return PERMUTO_ERR_INVALID_ARGUMENT;
-    if (reinterpret_cast<uintptr_t>(region) % 16 != 0) return PERMUTO_ERR_INVALID_ARGUMENT;
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        return PERMUTO_ERR_CUDA;
+    if (region_bytes < entry_bytes || region_bytes / entry_bytes > 0x7fffffffLL)
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "probe: region_bytes out of range");
+    if (reinterpret_cast<uintptr_t>(region) % 16 != 0)
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "probe: region must be 16-byte aligned");
+    const int sms = permuto::sm_count();
+    if (sms <= 0) return set_error(PERMUTO_ERR_CUDA, "probe: cannot query the device");
     const int blocks = sms * 32;
     const uint32_t entries = (uint32_t)(region_bytes / entry_bytes);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -78,5 +85,6 @@ extern "C" int permuto_probe_random_access(int32_t kind, float* region, int64_t 
         default: probe_kernel<3><<<blocks, 256, 0, st>>>(region, entries, accesses_per_thread); break;
     }
     if (total_accesses) *total_accesses = (int64_t)blocks * 256 * accesses_per_thread;
-    return cudaGetLastError() == cudaSuccess ? PERMUTO_OK : PERMUTO_ERR_CUDA;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? PERMUTO_OK : set_error(PERMUTO_ERR_CUDA, "probe launch: %s", cudaGetErrorString(e));
 }

@@ -64,62 +64,116 @@ class LatticeGradAllReduce:
     level buckets and all-reduces each bucket while the next one is being computed.
 
     After ``loss.backward()`` the parameter's ``.grad`` holds the sum over ranks (or the mean
-    with ``average=True``).  Call ``remove()`` to restore single-GPU behaviour.
+    with ``average=True``).  The second-order term of an eikonal loss -- the lattice gradient
+    that the double backward of the position gradient produces -- is all-reduced too, so the
+    replicated tables receive identical updates on every rank.  Call ``remove()`` to restore
+    single-GPU behaviour and release the communication buffers.
 
     Collective used: with NCCL on GPUs that share an NVSwitch multicast domain the buckets are
     reduced with ``multimem`` instructions (the switch adds the ranks' copies; PyTorch's
     symmetric-memory all-reduce) on a side stream -- measured on 8 B200s 0.25 ms for the 96 MB
     gradient against 0.32 ms for ``ncclAllReduce``, 0.055 against 0.097 ms for a 16 MB bucket;
     otherwise (``multimem=False``, gloo, no multicast support) ``dist.all_reduce(async_op=True)``.
+
+    With the symmetric-memory path the gradient handed to autograd is a *view* of one of two
+    persistent communication buffers used alternately (``copy_out=False``, the default): no
+    per-step allocation and no 100 MB copy out of the buffer.  The tensor stays valid until the
+    backward after the next one; a caller that keeps a gradient longer clones it or passes
+    ``copy_out=True``.  Gradient accumulation works: a buffer that the parameter's ``.grad``
+    still aliases is never the one written.
+
     Constructing the hook is a collective call when ``multimem`` is not False: every rank of the
-    group must construct it."""
+    group must construct it, and it blocks until all have.  The ranks first agree (a MIN
+    all-reduce of a flag) on whether symmetric memory can be tried at all, and only then enter
+    the symmetric-memory rendezvous together; they agree once more on its outcome."""
 
     def __init__(self, encoding, process_group=None, nr_buckets: int = 2, average: bool = False,
-                 policy: str = "halving", multimem="auto"):
+                 policy: str = "halving", multimem="auto", copy_out: bool = False, clear: str = "inline"):
+        if clear not in ("inline", "early"):
+            raise ValueError(f"clear must be 'inline' or 'early', got {clear!r}")
         self.encoding = encoding
         self.group = process_group
         self.average = average
+        self.copy_out = bool(copy_out)
+        self.clear = clear
         self.buckets = level_buckets(encoding.nr_levels, nr_buckets, policy)
-        self._symm = None
-        self._cleared = None
+        self._symm = None            # list of symmetric buffers (two, or one with copy_out)
+        self._next = 0               # buffer the next backward writes
+        self._precleared = -1        # buffer already zeroed off the critical path (clear="early")
+        self._done = None            # event: the last step's collectives (and copies) have finished
+        self._comm_stream = None
         self.multimem_error = None
         if multimem:
             self._try_symmetric_memory(encoding.lattice_values, required=(multimem is True))
         encoding.lattice.backward_hook = self._backward
+        encoding.lattice.double_backward_hook = self.reduce_second_order
         self.last_works = []
+
+    # -- set-up --------------------------------------------------------------------------------
+    def _agree(self, ok: bool, values, group) -> bool:
+        flag = torch.tensor([1 if ok else 0], device=values.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        return int(flag.item()) == 1
 
     def _try_symmetric_memory(self, values, required: bool) -> None:
         group = self.group if self.group is not None else dist.group.WORLD
-        usable = values.is_cuda and dist.get_world_size(group) > 1 and dist.get_backend(group) == "nccl"
-        buf = None
-        if usable:
+        if dist.get_world_size(group) < 2 or dist.get_backend(group) != "nccl":
+            self.multimem_error = "needs an NCCL group of at least two ranks"   # identical on every rank
+            if required:
+                raise RuntimeError("multimem all-reduce requested but " + self.multimem_error)
+            return
+        symm_mem = None
+        if values.is_cuda:
             try:
                 import torch.distributed._symmetric_memory as symm_mem
+            except Exception as exc:  # noqa: BLE001
+                self.multimem_error = repr(exc)
+        else:
+            self.multimem_error = "lattice values are not on a CUDA device"
+        # nobody enters the rendezvous unless everybody can
+        bufs = None
+        if self._agree(symm_mem is not None, values, group):
+            bufs, ok = [], True
+            for _ in range(1 if self.copy_out else 2):
                 buf = symm_mem.empty(values.numel(), dtype=torch.float32, device=values.device)
                 handle = symm_mem.rendezvous(buf, group)
                 if getattr(handle, "multicast_ptr", 1) == 0:  # no NVSwitch multicast object behind it
                     self.multimem_error = "symmetric memory has no multicast pointer"
-                    buf = None
-            except Exception as exc:  # noqa: BLE001 -- any failure means "use the NCCL path"
-                self.multimem_error = repr(exc)
-                buf = None
-        if usable:
-            # every rank must take the same path: agree on the weakest outcome
-            flag = torch.tensor([1 if buf is not None else 0], device=values.device, dtype=torch.int32)
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-            if int(flag.item()) == 0:
-                buf = None
-        if buf is None and required:
+                    ok = False
+                bufs.append(buf)
+            if not self._agree(ok, values, group):
+                bufs = None
+        elif self.multimem_error is None:
+            self.multimem_error = "another rank cannot use symmetric memory"
+        if bufs is None and required:
             raise RuntimeError("multimem all-reduce requested but symmetric memory with multicast is not available: "
                                f"{self.multimem_error}")
-        if buf is not None:
-            self._symm = buf
+        if bufs is not None:
+            self._symm = bufs
             self._group_name = group.group_name
             self._comm_stream = torch.cuda.Stream(values.device)
 
     def remove(self) -> None:
+        """Uninstall the hooks and release the symmetric buffers and the side stream.  Gradients
+        handed out as views of those buffers must not be used afterwards."""
         self.encoding.lattice.backward_hook = None
+        self.encoding.lattice.double_backward_hook = None
+        if self._comm_stream is not None:
+            self._comm_stream.synchronize()
+        self._symm = None
+        self._comm_stream = None
+        self._done = None
 
+    # -- second-order term -----------------------------------------------------------------------
+    def reduce_second_order(self, lattice_grad: torch.Tensor) -> torch.Tensor:
+        """All-reduce of the lattice gradient produced by the double backward (eikonal term); it
+        is added by autograd to the first-order gradient, which is already reduced."""
+        dist.all_reduce(lattice_grad, op=dist.ReduceOp.SUM, group=self.group)
+        if self.average:
+            lattice_grad.div_(dist.get_world_size(self.group))
+        return lattice_grad
+
+    # -- first-order backward ----------------------------------------------------------------------
     def _backward(self, lattice, input_struct, grad_features):
         values = input_struct.m_lattice_values
         if self._symm is not None:
@@ -141,40 +195,76 @@ class LatticeGradAllReduce:
         self.last_works = works
         return lv_grad, pos_grad
 
+    def _pick_buffer(self) -> int:
+        """Index of the symmetric buffer this backward writes: the two alternate, except that a
+        buffer still aliased by the parameter's ``.grad`` (gradient accumulation) is skipped."""
+        if len(self._symm) == 1:
+            return 0
+        i = self._next
+        held = getattr(self.encoding.lattice_values, "grad", None) if hasattr(self.encoding, "lattice_values") else None
+        if held is not None and held.is_cuda and \
+                held.untyped_storage().data_ptr() == self._symm[i].untyped_storage().data_ptr():
+            i ^= 1
+        self._next = i ^ 1
+        return i
+
     def _backward_multimem(self, lattice, input_struct, grad_features, values):
         """Buckets are computed on the caller's stream into a persistent symmetric buffer; a side
-        stream all-reduces each finished bucket in place, copies it into the tensor handed to
-        autograd (the buffer is overwritten by the next backward), beside the following bucket's
-        backward kernel.  Only the last bucket's all-reduce and copy are exposed.  The buffer is
-        cleared inside each bucket's backward call, right before its kernel: clearing it early (at
-        the end of the previous step) was measured 10 % slower end to end, because the memset is
-        also what brings the gradient slices into L2 ahead of the reductions."""
-        lv = self._symm.view(values.shape)          # same allocation on every rank
+        stream all-reduces each finished bucket in place beside the following bucket's backward
+        kernel, so only the last bucket's all-reduce is exposed.  The buffer is cleared inside each
+        bucket's backward call, right before its kernel (``clear="inline"``), or -- ``clear="early"``
+        -- the buffer of the *next* step is cleared on the side stream while this step's first
+        bucket is being computed."""
+        i = self._pick_buffer()
+        lv = self._symm[i].view(values.shape)        # same allocation on every rank
         current = torch.cuda.current_stream(values.device)
         comm = self._comm_stream
-        out = torch.empty_like(values)
-        out.record_stream(comm)
-        if self._cleared is not None:
-            current.wait_event(self._cleared)       # the previous step's copies out of the buffer
+        out = lv
+        if self.copy_out:
+            out = torch.empty_like(values)
+            out.record_stream(comm)
+            if self._done is not None:
+                current.wait_event(self._done)      # the previous step's copies out of the buffer
         scale = 1.0 / dist.get_world_size(self.group) if self.average else None
+        inline_clear = not (self.clear == "early" and self._precleared == i)
+        early_next = self.clear == "early" and len(self._symm) == 2
         pos_grad = None
-        for l0, l1 in self.buckets:
+        for b, (l0, l1) in enumerate(self.buckets):
+            if b == 0 and early_next:
+                # everything that read the other buffer (the gradient of the step before) was
+                # enqueued on the caller's stream before this point
+                start = torch.cuda.Event()
+                start.record(current)
+                comm.wait_event(start)
+                held = self.encoding.lattice_values.grad
+                other = self._symm[i ^ 1]
+                if held is None or held.untyped_storage().data_ptr() != other.untyped_storage().data_ptr():
+                    with torch.cuda.stream(comm):
+                        other.zero_()
+                    self._precleared = i ^ 1
+                else:
+                    self._precleared = -1
             _, pg = lattice.backward(input_struct, grad_features, lattice_grad_out=lv, level_begin=l0,
-                                     level_end=l1, zero=True, positions_grad_out=pos_grad)
+                                     level_end=l1, zero=inline_clear, positions_grad_out=pos_grad)
             pos_grad = pg if pg is not None else pos_grad
             ready = torch.cuda.Event()
             ready.record(current)
             comm.wait_event(ready)
             with torch.cuda.stream(comm):
                 torch.ops.symm_mem.multimem_all_reduce_(lv[l0:l1].reshape(-1), "sum", self._group_name)
-                if scale is None:
-                    out[l0:l1].copy_(lv[l0:l1])
-                else:
-                    torch.mul(lv[l0:l1], scale, out=out[l0:l1])
+                if self.copy_out:
+                    if scale is None:
+                        out[l0:l1].copy_(lv[l0:l1])
+                    else:
+                        torch.mul(lv[l0:l1], scale, out=out[l0:l1])
+                elif scale is not None:
+                    lv[l0:l1].mul_(scale)
+        if not inline_clear:
+            self._precleared = -1 if not early_next else self._precleared
         done = torch.cuda.Event()
         done.record(comm)
         current.wait_event(done)
-        self._cleared = done
+        self._done = done
         return out, pos_grad
 
 

@@ -16,18 +16,29 @@ class PermutoEncoding(torch.nn.Module):
     then feature (reference: modules.py:65-93).  Parameters, as in the reference so that its
     checkpoints load unchanged: ``lattice_values`` fp32 ``[nr_levels, capacity, nr_feat_per_level]``
     and ``random_shift_per_level`` fp32 ``[nr_levels, pos_dim]`` (never receives a gradient).
+    One exception: with ``appply_random_shift_per_level=False`` the reference stores a 1-element
+    shift; such a checkpoint entry is accepted and read as the zero shift.
     The misspelt keyword ``appply_random_shift_per_level`` is part of the reference's public
     surface and is kept.  With ``appply_random_shift_per_level=False`` the reference creates an
     unusable 1-element shift (modules.py:34 fails the native shape checks); here the shift is
     a zero ``[nr_levels, pos_dim]`` tensor, which is what the flag means.
     ``nr_feat_per_level`` may be 2 (the only width the reference implements), 4 or 8: a table
-    access moves a 32-byte sector whatever it uses of it, and 16-byte accesses run at the rate of
-    8-byte ones, so e.g. 12 levels of 4 features produce 48 outputs in 60 % of the time of 24 x 2.
+    access moves a 32-byte sector whatever it uses of it, and a random access costs about the same
+    whether it moves 8 or 16 bytes, so e.g. 12 levels of 4 features produce 48 outputs in 60 % of
+    the time of 24 x 2.
+    ``half_precision_table=True`` (not in the reference, which only hints at it,
+    kernels/permutohedral_encoding/EncodingGPU.cuh:12) makes the kernels gather from an fp16 copy
+    of ``lattice_values``: storage only -- products, sums, outputs, the parameter, its gradient
+    and the optimizer state stay fp32 -- so the table takes half the room in L2 and a 4-feature
+    entry is the 8 bytes a 2-feature fp32 entry is.
     """
 
     def __init__(self, pos_dim, capacity, nr_levels, nr_feat_per_level, scale_per_level,
-                 appply_random_shift_per_level=True, concat_points=False, concat_points_scaling=1.0):
+                 appply_random_shift_per_level=True, concat_points=False, concat_points_scaling=1.0,
+                 half_precision_table=False):
         super().__init__()
+        self.half_precision_table = bool(half_precision_table)
+        self._half, self._half_version, self._half_ptr = None, -1, 0
         self.pos_dim = pos_dim
         self.capacity = capacity
         self.nr_levels = nr_levels
@@ -61,6 +72,7 @@ class PermutoEncoding(torch.nn.Module):
         state = self.__dict__.copy()
         del state["fixed_params"]  # native-side objects are rebuilt, not pickled
         del state["lattice"]
+        state["_half"], state["_half_version"], state["_half_ptr"] = None, -1, 0  # the fp16 copy is rebuilt on first use
         return state
 
     def __setstate__(self, state):
@@ -68,11 +80,28 @@ class PermutoEncoding(torch.nn.Module):
         self.fixed_params, self.lattice = self._make_lattice_wrapper()
 
     def _apply(self, fn, *args, **kwargs):
-        # .to()/.cuda() may replace the parameter objects: re-bind the shift handle
+        # .to()/.cuda() may replace the parameter objects: re-bind the shift handle.  The kernels
+        # compute in fp32 only, so a dtype conversion (.half(), .double()) is refused here, where
+        # it is asked for, instead of surfacing later as a shape/dtype error inside a call.
+        if fn(torch.empty(0, dtype=torch.float32, device=self.lattice_values.device)).dtype != torch.float32:
+            raise RuntimeError("PermutoEncoding computes in float32 only: lattice_values and "
+                               "random_shift_per_level cannot be converted to another dtype")
         out = super()._apply(fn, *args, **kwargs)
-        self.anneal_window = fn(self.anneal_window)
+        # the window follows device moves only
+        self.anneal_window = fn(self.anneal_window).to(torch.float32)
         self.fixed_params.m_random_shift_per_level = self.random_shift_per_level
         return out
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        # A reference checkpoint saved with appply_random_shift_per_level=False holds an
+        # uninitialised 1-element shift (reference: modules.py:34); here that flag means a zero
+        # shift of the regular shape, so such an entry is read as zeros.
+        key = prefix + "random_shift_per_level"
+        value = state_dict.get(key)
+        if value is not None and tuple(value.shape) == (1,) and not self.appply_random_shift_per_level:
+            state_dict = dict(state_dict)
+            state_dict[key] = torch.zeros_like(self.random_shift_per_level)
+        return super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
     def forward(self, positions, anneal_window=None):
         if anneal_window is None:
@@ -82,17 +111,31 @@ class PermutoEncoding(torch.nn.Module):
         # the shift parameter may have been replaced (load_state_dict(assign=True), .to())
         self.fixed_params.m_random_shift_per_level = self.random_shift_per_level
 
+        half = self._half_copy() if getattr(self, "half_precision_table", False) else None
         grad_mode = torch.is_grad_enabled()
         require_lattice_values_grad = self.lattice_values.requires_grad and grad_mode
         require_positions_grad = positions.requires_grad and grad_mode
         if not (require_lattice_values_grad or require_positions_grad):
             # inference: nothing to record, skip the autograd machinery (host overhead dominates
             # README-sized batches)
-            return self.lattice.forward(_C.EncodingInput(self.lattice_values, positions, anneal_window, False, False))
+            return self.lattice.forward(_C.EncodingInput(self.lattice_values, positions, anneal_window, False, False,
+                                                         half))
 
         # [N, (L+extra)*F] already in the reference's output order: no permute/reshape copy
         return PermutoEncodingFunc.apply(self.lattice, self.lattice_values, positions, anneal_window,
-                                         require_lattice_values_grad, require_positions_grad)
+                                         require_lattice_values_grad, require_positions_grad, half)
+
+    def _half_copy(self):
+        """fp16 copy of the lattice values the kernels gather from when ``half_precision_table`` is
+        set; re-made whenever the parameter has been modified in place (an optimizer step) or
+        replaced.  The parameter, its gradient and the optimizer state stay fp32."""
+        v = self.lattice_values
+        if self._half is None or self._half_version != v._version or self._half.device != v.device \
+                or self._half_ptr != v.data_ptr():
+            self._half = v.detach().to(torch.float16)
+            self._half_version = v._version
+            self._half_ptr = v.data_ptr()
+        return self._half
 
     def output_dims(self):
         nr_resolutions_extra = 0

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol(nat):
     assert len(names) >= 8
     for n in names:
         assert hasattr(nat.lib, n), f"{n} declared in include/permuto_b200.h but not exported"
-    assert nat.lib.permuto_abi_version() == 1
+    assert nat.lib.permuto_abi_version() == nat.ABI_VERSION == 2
 
 
 def test_extra_levels(nat):
@@ -60,14 +60,14 @@ def test_argument_validation_without_gpu(nat):
     lib = nat.lib
     assert lib.permuto_forward(None, None, None, None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
     assert "NULL" in nat.last_error()
-    cfg = nat.PermutoConfig(8, 2, 4, 1024, 0, 1.0, 0)
+    cfg = nat.PermutoConfig(8, 2, 4, 1024, 0, 1.0, 0, 0)
     ins = nat.PermutoInputs(10, 8, 3, 1, 8, 8, 8, 8)
     assert lib.permuto_forward(C.byref(cfg), C.byref(ins), C.c_void_p(8), None) == nat.PERMUTO_ERR_UNSUPPORTED
     assert "pos_dim must be 2,3,4,5,6 or 7" in nat.last_error()
-    cfg = nat.PermutoConfig(3, 3, 4, 1024, 0, 1.0, 0)
+    cfg = nat.PermutoConfig(3, 3, 4, 1024, 0, 1.0, 0, 0)
     assert lib.permuto_forward(C.byref(cfg), C.byref(ins), C.c_void_p(8), None) == nat.PERMUTO_ERR_UNSUPPORTED
     assert "nr_feat_per_level must be 2, 4 or 8" in nat.last_error()
-    cfg = nat.PermutoConfig(3, 2, 4, 1024, 0, 1.0, 0)
+    cfg = nat.PermutoConfig(3, 2, 4, 1024, 0, 1.0, 0, 0)
     ins0 = nat.PermutoInputs(0, 8, 3, 1, 8, 8, 8, 8)
     assert lib.permuto_forward(C.byref(cfg), C.byref(ins0), C.c_void_p(8), None) == nat.PERMUTO_ERR_INVALID_ARGUMENT
     assert "0 points" in nat.last_error()

@@ -130,3 +130,105 @@ def test_gradient_hook_buckets_and_averages_two_ranks(tmp_path):
     assert h0["calls"] == [(0, 4), (4, 8), (8, 10)] and h0["pos"] is None
     want = 1.5 * (1 + torch.arange(10)).view(-1, 1, 1).float().expand(10, 8, 2)   # mean of 1x and 2x
     assert torch.equal(h0["grad"], h1["grad"]) and torch.allclose(h0["grad"], want)
+
+
+class _BilinearLattice:
+    """CPU stand-in for the native wrapper with the same three operations on a bilinear toy model:
+    features[n, 2l+f] = positions[n, 0] * values[l, 0, f].  Small enough to differentiate by hand,
+    rich enough to have a second-order term through the position gradient."""
+
+    def __init__(self):
+        self.backward_hook = None
+        self.double_backward_hook = None
+
+    def forward(self, inp):
+        return inp.m_positions_raw[:, :1] * inp.m_lattice_values.reshape(1, -1)
+
+    def backward(self, inp, grad_features, lattice_grad_out=None, level_begin=None, level_end=None, zero=True,
+                 positions_grad_out=None):
+        v, x = inp.m_lattice_values, inp.m_positions_raw
+        lb = 0 if level_begin is None else level_begin
+        le = v.shape[0] if level_end is None else level_end
+        lg = lattice_grad_out if lattice_grad_out is not None else torch.zeros_like(v)
+        g = grad_features.reshape(x.shape[0], v.shape[0], 2)
+        lg[lb:le, 0, :] = (x[:, :1, None] * g[:, lb:le, :]).sum(0)
+        pg = None
+        if inp.m_require_positions_grad:
+            pg = positions_grad_out if positions_grad_out is not None else torch.zeros_like(x)
+            pg[:, 0] += (g[:, lb:le, :] * v[None, lb:le, 0, :]).sum((1, 2))
+        return (lg if inp.m_require_lattice_values_grad else None), pg
+
+    def double_backward_from_positions(self, inp, dpg, grad_features, need_lattice_grad=True,
+                                       need_grad_grad_features=True):
+        v, x = inp.m_lattice_values, inp.m_positions_raw
+        g = grad_features.reshape(x.shape[0], v.shape[0], 2)
+        lg = (dpg[:, :1, None] * g).sum(0).reshape(v.shape) if need_lattice_grad else None
+        ggf = (dpg[:, :1] * v.reshape(1, -1)) if need_grad_grad_features else None
+        return lg, ggf
+
+
+class _BilinearEncoding:
+    def __init__(self, values):
+        self.nr_levels = values.shape[0]
+        self.lattice_values = values
+        self.lattice = _BilinearLattice()
+
+
+def _eikonal_grad(values, pos, w, hook_owner=None, n_total=None):
+    """lattice_values.grad of mean((|d(F w)/dx| - 1)^2) + mean(F^2) through the package's two
+    autograd Functions, on the toy lattice."""
+    import permutohedral_encoding_b200.funcs as funcs
+
+    class _Input:   # the Functions build EncodingInput through the native module: replace it for CPU tensors
+        def __init__(self, lv, p, aw, a, b, half=None):
+            self.m_lattice_values, self.m_positions_raw, self.m_anneal_window = lv, p, aw
+            self.m_require_lattice_values_grad, self.m_require_positions_grad = bool(a), bool(b)
+
+    real = funcs._C.EncodingInput
+    funcs._C.EncodingInput = _Input
+    try:
+        enc = hook_owner if hook_owner is not None else _BilinearEncoding(values)
+        x = pos.clone().requires_grad_(True)
+        out = funcs.PermutoEncodingFunc.apply(enc.lattice, values, x, torch.ones(values.shape[0]), True, True)
+        (g,) = torch.autograd.grad((out @ w).sum(), x, create_graph=True)
+        n = n_total if n_total is not None else pos.shape[0]
+        loss = ((g.norm(dim=1) - 1.0) ** 2).sum() / n + out.square().sum() / n
+        loss.backward()
+        return values.grad.clone()
+    finally:
+        funcs._C.EncodingInput = real
+
+
+def _second_order_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from permutohedral_encoding_b200.distributed import LatticeGradAllReduce, shard_bounds
+    gen = torch.Generator().manual_seed(11)
+    L, n = 6, 40
+    init = torch.randn(L, 1, 2, generator=gen)
+    pos_all = torch.randn(n, 3, generator=gen)
+    w = torch.randn(2 * L, generator=gen)
+    full = _eikonal_grad(init.clone().requires_grad_(True), pos_all, w)          # whole batch, no hook
+    values = init.clone().requires_grad_(True)
+    enc = _BilinearEncoding(values)
+    hook = LatticeGradAllReduce(enc, nr_buckets=2, multimem=False)
+    b, e = shard_bounds(n, rank, world)
+    sharded = _eikonal_grad(values, pos_all[b:e], w, hook_owner=enc, n_total=n)
+    hook.remove()
+    assert enc.lattice.backward_hook is None and enc.lattice.double_backward_hook is None
+    torch.save({"full": full, "sharded": sharded}, os.path.join(out_dir, f"s{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_second_order_lattice_gradient_is_reduced_two_ranks(tmp_path):
+    """Eikonal-style step on two gloo ranks: the lattice gradient from the double backward goes
+    through the same sum over ranks as the first-order one, so every rank ends with the gradient
+    of the whole batch."""
+    port = _free_port()
+    mp.spawn(_second_order_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    s0, s1 = torch.load(tmp_path / "s0.pt"), torch.load(tmp_path / "s1.pt")
+    assert torch.allclose(s0["sharded"], s0["full"], rtol=1e-5, atol=1e-6)
+    assert torch.allclose(s1["sharded"], s0["full"], rtol=1e-5, atol=1e-6)
+    assert torch.equal(s0["sharded"], s1["sharded"])

@@ -23,7 +23,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, out_dir, use_multimem):
+def _worker(rank, world, port, out_dir, use_multimem, copy_out, clear):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
@@ -49,7 +49,7 @@ def _worker(rank, world, port, out_dir, use_multimem):
     full_tg, full_pg = m.lattice_values.grad.clone(), pos.grad.clone()
     m.lattice_values.grad = None
     # this rank's shard with the bucketed all-reduce
-    hook = LatticeGradAllReduce(m, nr_buckets=3, multimem=use_multimem)
+    hook = LatticeGradAllReduce(m, nr_buckets=3, multimem=use_multimem, copy_out=copy_out, clear=clear)
     b, e = shard_bounds(n, rank, world)
     pos_s = pos_all[b:e].clone().requires_grad_(True)
     out_s = m(pos_s)
@@ -59,20 +59,46 @@ def _worker(rank, world, port, out_dir, use_multimem):
     ok_tg = bool(torch.all((m.lattice_values.grad - full_tg).abs() <= 1e-4 * lvl))
     ok_out = bool(torch.equal(out_s, out_full[b:e]))
     ok_pg = bool(torch.all((pos_s.grad - full_pg[b:e]).abs() <= 1e-4 * full_pg.abs().max()))
+    # gradient accumulation: a second backward without clearing .grad doubles it (the buffer that
+    # .grad aliases is never the one the next backward writes)
+    out_s2 = m(pos_all[b:e])
+    out_s2.backward(go_all[b:e])
+    torch.cuda.synchronize()
+    ok_acc = bool(torch.all((m.lattice_values.grad - 2 * full_tg).abs() <= 2e-4 * lvl))
+    # eikonal step: the second-order lattice gradient is summed over the ranks too
+    w = torch.randn(2 * nl, generator=gen).to(dev) * 0.2
+
+    def eikonal(points, n_total):
+        m.lattice_values.grad = None
+        x = points.clone().requires_grad_(True)
+        y = m(x)
+        (g,) = torch.autograd.grad((y @ w).sum(), x, create_graph=True)
+        (((g.norm(dim=1) - 1.0) ** 2).sum() / n_total + y.square().sum() / n_total).backward()
+        torch.cuda.synchronize()
+        return m.lattice_values.grad.clone()
+
+    sharded_e = eikonal(pos_all[b:e], n)
     hook.remove()
-    torch.save({"ok": (ok_tg, ok_out, ok_pg)}, os.path.join(out_dir, f"r{rank}.pt"))
+    full_e = eikonal(pos_all, n)
+    lvl_e = full_e.abs().amax(dim=(1, 2), keepdim=True)
+    ok_eik = bool(torch.all((sharded_e - full_e).abs() <= 2e-4 * lvl_e))
+    torch.save({"ok": (ok_tg, ok_out, ok_pg, ok_acc, ok_eik)}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_multimem", [False, "auto"])
-def test_sharded_step_matches_single_gpu(tmp_path, use_multimem):
+@pytest.mark.parametrize("use_multimem,copy_out,clear", [(False, False, "inline"), ("auto", False, "inline"),
+                                                         ("auto", True, "inline"), ("auto", False, "early")])
+def test_sharded_step_matches_single_gpu(tmp_path, use_multimem, copy_out, clear):
+    """First-order step, gradient accumulation and an eikonal (double-backward) step on two ranks
+    against the same batch on one GPU; NCCL all-reduce and the in-switch (multimem) path, the
+    latter handing out views of its buffers, copies, and with the early clearing."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     port = _free_port()
-    mp.spawn(_worker, args=(2, port, str(tmp_path), use_multimem), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), use_multimem, copy_out, clear), nprocs=2, join=True)
     for r in range(2):
-        assert torch.load(tmp_path / f"r{r}.pt")["ok"] == (True, True, True)
+        assert torch.load(tmp_path / f"r{r}.pt")["ok"] == (True, True, True, True, True)
 
 
 def test_module_on_a_device_that_is_not_current():

@@ -183,3 +183,27 @@ def test_oracle_identities_wider_features(oracle, feat):
     y = float((db["table_grad"].astype(np.float64) * inp["table"]).sum())
     z = float((db["grad_grad_out"].astype(np.float64) * inp["grad_out"]).sum())
     assert abs(x - y) <= 1e-4 * (abs(x) + 1) and abs(x - z) <= 1e-4 * (abs(x) + 1)
+
+
+@pytest.mark.parametrize("hyper", [dict(lr=1e-3, betas=(0.9, 0.99), eps=1e-15, weight_decay=0.0),
+                                   dict(lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2)])
+def test_adam_oracle_matches_torch_adamw(hyper):
+    """The numpy restatement of the table's optimizer step against torch.optim.AdamW itself (CPU
+    tensors), with the hyper-parameters of the reference's two training scripts."""
+    import torch
+    from oracle import adam_oracle
+    rng = np.random.default_rng(3)
+    p0 = (rng.standard_normal((3, 50, 2)) * 1e-4).astype(np.float32)
+    param = torch.nn.Parameter(torch.from_numpy(p0.copy()))
+    opt = torch.optim.AdamW([param], amsgrad=False, foreach=False, **hyper)
+    p, m, v = p0.copy(), np.zeros_like(p0), np.zeros_like(p0)
+    for step in range(1, 8):
+        g = (rng.standard_normal(p0.shape) * (rng.random(p0.shape) < 0.6)).astype(np.float32)  # some exact zeros
+        param.grad = torch.from_numpy(g.copy())
+        opt.step()
+        p, m, v = adam_oracle.adamw_step(p, g, m, v, step, hyper["lr"], hyper["betas"][0], hyper["betas"][1],
+                                         hyper["eps"], hyper["weight_decay"])
+        np.testing.assert_allclose(p, param.detach().numpy(), rtol=1e-6, atol=1e-6 * hyper["lr"])
+        st = opt.state[param]
+        np.testing.assert_allclose(m, st["exp_avg"].numpy(), rtol=1e-6, atol=1e-7)
+        np.testing.assert_allclose(v, st["exp_avg_sq"].numpy(), rtol=1e-6, atol=1e-7)
