@@ -113,6 +113,22 @@ int permuto_scale_factor(const double *sigmas, int32_t nr_levels, int32_t pos_di
  * module's permute/reshape copy (src/pytorch_modules/modules.py:87). */
 int permuto_forward(const permuto_config *cfg, const permuto_inputs *in, float *features, void *stream);
 
+/* Forward fused with the first linear layer of the network that consumes the features:
+ *     out[N, out_features] = features[N, W] @ weight[out_features, W]^T + bias
+ * without the features ever being written to memory.  The reference's users run exactly this pair
+ * (examples/train_toy_example.py:18-26, README.md:39-40: PermutoEncoding followed by
+ * torch.nn.Linear(encoding.output_dims(), 32)); the reference itself has no fused form.
+ * weight is row-major [out_features, W] (the layout of torch.nn.Linear.weight), bias [out_features]
+ * or NULL, out_features a multiple of 16 in 16..256, W = F*(L + extra_levels) at most 256.
+ * The product runs on the tensor cores with both operands rounded to tf32 (10-bit mantissa) and
+ * fp32 accumulation: |out - exact| <= about 1e-3 * sum_k |features_k * weight_k| per output.
+ * status, if not NULL, is a device int32 the kernel sets non-zero when its bounded wait for the
+ * tensor core ran out (it then writes no output for that block); the caller clears and reads it.
+ * Inference path: no gradients are produced. */
+int permuto_forward_linear(const permuto_config *cfg, const permuto_inputs *in, const float *weight,
+                           const float *bias, int32_t out_features, float *out, int32_t *status,
+                           void *stream);
+
 /* First-order backward.  Replaces Encoding<P,2>::backward (src/Encoding.cu:111-215).
  * grad_features [N, W].  lattice_grad and positions_grad may each be NULL (not required).
  * Only levels in [level_begin, level_end) are processed -- pass 0 and nr_levels for all; a

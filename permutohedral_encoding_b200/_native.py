@@ -40,7 +40,7 @@ PERMUTO_ADAM_ZERO_GRAD = 2
 EXPORTED_SYMBOLS = (
     "permuto_abi_version", "permuto_last_error", "permuto_extra_levels", "permuto_scale_factor",
     "permuto_forward", "permuto_backward", "permuto_double_backward", "permuto_debug_lattice",
-    "permuto_probe_random_access", "permuto_adam_step",
+    "permuto_probe_random_access", "permuto_adam_step", "permuto_forward_linear",
 )
 
 
@@ -83,6 +83,8 @@ def _load() -> C.CDLL:
     lib.permuto_probe_random_access.restype = C.c_int
     lib.permuto_probe_random_access.argtypes = [C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.POINTER(C.c_int64),
                                                 C.c_void_p]
+    lib.permuto_forward_linear.restype = C.c_int
+    lib.permuto_forward_linear.argtypes = [cfgp, inp, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.permuto_adam_step.restype = C.c_int
     lib.permuto_adam_step.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_double, C.c_double,
                                       C.c_double, C.c_double, C.c_double, C.c_int64, C.c_uint32, C.c_void_p]
@@ -304,6 +306,40 @@ class EncodingWrapper:
         with _guard(pos.device):
             ins, keep = self._inputs(inp)
             check(lib.permuto_forward(C.byref(cfg), C.byref(ins), _ptr(out), _stream(pos.device)))
+        return out
+
+    def forward_linear(self, inp: EncodingInput, weight: torch.Tensor, bias=None, status=None) -> torch.Tensor:
+        """``features @ weight.T + bias`` as ``[N, out_features]`` without materialising the features
+        (tensor cores, operands rounded to tf32, fp32 accumulation).  ``weight`` is
+        ``[out_features, output_width]`` like ``torch.nn.Linear.weight``; ``status`` is an optional
+        int32 CUDA tensor of one element that the kernel sets non-zero if its bounded wait for the
+        tensor core ran out.  No gradients.  The reference has no counterpart (its users run the
+        module followed by ``torch.nn.Linear``: examples/train_toy_example.py:18-26)."""
+        self._check(inp)
+        pos = inp.m_positions_raw
+        dev = pos.device
+        if weight.dim() != 2 or weight.shape[1] != self.output_width():
+            raise RuntimeError(f"weight should be out_features x {self.output_width()}, got {tuple(weight.shape)}")
+        h = int(weight.shape[0])
+        if h % 16 != 0 or not (16 <= h <= 256):
+            raise RuntimeError(f"out_features must be a multiple of 16 in 16..256 (got {h})")
+        weight = weight.detach()
+        if weight.device != dev or weight.dtype != torch.float32 or not weight.is_contiguous():
+            weight = weight.to(device=dev, dtype=torch.float32).contiguous()
+        if bias is not None:
+            bias = bias.detach()
+            if tuple(bias.shape) != (h,):
+                raise RuntimeError(f"bias should have {h} entries")
+            if bias.device != dev or bias.dtype != torch.float32 or not bias.is_contiguous():
+                bias = bias.to(device=dev, dtype=torch.float32).contiguous()
+        if status is not None and (status.dtype != torch.int32 or status.device != dev or status.numel() != 1):
+            raise RuntimeError("status should be a one-element int32 tensor on the device of the positions")
+        cfg = self._config(inp)
+        out = torch.empty((pos.shape[0], h), dtype=torch.float32, device=dev)
+        with _guard(dev):
+            ins, keep = self._inputs(inp)
+            check(lib.permuto_forward_linear(C.byref(cfg), C.byref(ins), _ptr(weight), _ptr(bias), h, _ptr(out),
+                                             _ptr(status), _stream(dev)))
         return out
 
     def backward(self, inp: EncodingInput, grad_features: torch.Tensor, lattice_grad_out=None,

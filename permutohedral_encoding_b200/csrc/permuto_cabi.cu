@@ -169,6 +169,31 @@ int permuto_forward(const permuto_config* cfg, const permuto_inputs* in, float* 
     return PERMUTO_OK;
 }
 
+int permuto_forward_linear(const permuto_config* cfg, const permuto_inputs* in, const float* weight, const float* bias,
+                           int32_t out_features, float* out, int32_t* status, void* stream) {
+    permuto::ForwardLinearArgs a;
+    if (int rc = build_problem(cfg, in, a.p)) return rc;
+    if (!weight || !out) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "weight and out must not be NULL");
+    if (out_features < 16 || out_features > 256 || out_features % 16 != 0)
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "out_features must be a multiple of 16 in 16..256 (got %d)", out_features);
+    if (a.p.width > 256)
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "the fused layer takes feature rows of at most 256 columns (got %d)",
+                         a.p.width);
+    if (!aligned(out, 16) || !aligned(weight, 4))
+        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "out must be 16-byte aligned");
+    a.weight = weight;
+    a.bias = bias;
+    a.out = out;
+    a.out_features = out_features;
+    a.k_pad = (a.p.width + 7) / 8 * 8;
+    a.status = status;
+    cudaError_t err;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PERMUTO_DISPATCH(launch_forward_linear, a, st)
+    if (err != cudaSuccess) return cuda_fail(err, "permuto_forward_linear launch");
+    return PERMUTO_OK;
+}
+
 int permuto_backward(const permuto_config* cfg, const permuto_inputs* in, const float* grad_features,
                      float* lattice_grad, float* positions_grad, int32_t level_begin, int32_t level_end,
                      uint32_t flags, void* stream) {

@@ -236,6 +236,40 @@ __device__ __forceinline__ void store_row_segment(const Problem& p, float* rows,
 // ------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------
+// One step of a point's feature row: LPS levels of F features (8 floats) starting at level l0;
+// levels at or beyond `end` give zeros (EncodingGPU.cuh:130-254 for one level).
+template <int F, int LPS, bool HALF>
+__device__ __forceinline__ void encode_step(const Problem& p, const float (&pos)[D], int l0, int end,
+                                            float (&out)[F * LPS]) {
+#pragma unroll
+    for (int k = 0; k < LPS; ++k) {
+        const int l = l0 + k;
+        float acc[F];
+#pragma unroll
+        for (int f = 0; f < F; ++f) acc[f] = 0.f;
+        if (l < end) {  // uniform over the block
+            const float w_lvl = __ldg(p.anneal + l);
+            if (w_lvl != 0.0f) {  // a closed coarse-to-fine window contributes exact zeros
+                Simplex<D> s;
+                locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
+                uint32_t slot[D + 1];
+                to_slots(p, s, slot);
+                float v[D + 1][F];
+#pragma unroll
+                for (int r = 0; r <= D; ++r) gather<F, HALF>(p.table, l, p.capacity, slot[r], v[r]);
+#pragma unroll
+                for (int r = 0; r <= D; ++r) {
+                    const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:234
+#pragma unroll
+                    for (int f = 0; f < F; ++f) acc[f] = fmaf(v[r][f], w, acc[f]);
+                }
+            }
+        }
+#pragma unroll
+        for (int f = 0; f < F; ++f) out[F * k + f] = acc[f];
+    }
+}
+
 template <int F, int LPS, bool HALF>
 __global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD : min_blocks(F, false))) forward_kernel(const ForwardArgs a) {
     const Problem& p = a.p;
@@ -250,33 +284,7 @@ __global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD
 #pragma unroll 1
     for (int l0 = pass_begin; l0 < pass_end; l0 += LPS) {
         float out[F * LPS];
-#pragma unroll
-        for (int k = 0; k < LPS; ++k) {
-            const int l = l0 + k;
-            float acc[F];
-#pragma unroll
-            for (int f = 0; f < F; ++f) acc[f] = 0.f;
-            if (l < pass_end) {  // uniform over the block
-                const float w_lvl = __ldg(p.anneal + l);
-                if (w_lvl != 0.0f) {  // a closed coarse-to-fine window contributes exact zeros
-                    Simplex<D> s;
-                    locate_simplex<D>(pos, p.shift + l * D, p.scale + l * D, s);
-                    uint32_t slot[D + 1];
-                    to_slots(p, s, slot);
-                    float v[D + 1][F];
-#pragma unroll
-                    for (int r = 0; r <= D; ++r) gather<F, HALF>(p.table, l, p.capacity, slot[r], v[r]);
-#pragma unroll
-                    for (int r = 0; r <= D; ++r) {
-                        const float w = s.bary[r] * w_lvl;  // EncodingGPU.cuh:234
-#pragma unroll
-                        for (int f = 0; f < F; ++f) acc[f] = fmaf(v[r][f], w, acc[f]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int f = 0; f < F; ++f) out[F * k + f] = acc[f];
-        }
+        encode_step<F, LPS, HALF>(p, pos, l0, pass_end, out);
         store_row_segment<F, LPS>(p, a.features, n, l0, out);
     }
 
@@ -290,6 +298,213 @@ __global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD
             dst[c] = v;
         }
     }
+}
+
+// ------------------------------------------------------------------------------------------
+// forward fused with the consumer's first linear layer (tcgen05 + TMEM)
+// ------------------------------------------------------------------------------------------
+// The users of the encoding feed the [N, F*L] feature row straight into a small MLP (reference:
+// examples/train_toy_example.py:18-26, README.md:39-40).  Here a block of 128 threads encodes 128
+// points, keeps the 128 x K feature tile in shared memory (K = F*(L+extra), rounded to tf32) and
+// multiplies it by the layer's weight [H, K] on the tensor cores: K/8 tcgen05.mma of shape
+// 128 x H x 8 (kind::tf32, fp32 accumulate) issued by one thread, accumulator in tensor memory,
+// read back with tcgen05.ld (thread t holds row t) and written as [N, H] with the bias added.
+// The 192 B/point feature row and the separate GEMM's read of it never touch HBM.
+//
+// Shared-memory operand layout (K-major, no swizzle -- the canonical layout of the tcgen05
+// matrix descriptor): 8 rows x 16 bytes form a contiguous 128-byte core matrix; the core
+// matrices of consecutive 4-column groups follow each other (leading byte offset 128) and those
+// of consecutive 8-row groups are K/4 * 128 bytes apart (stride byte offset).
+namespace umma {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// 64-bit shared-memory matrix descriptor: start address, leading / stride byte offsets (all in
+// units of 16 bytes), descriptor version 1 (Blackwell), no swizzle
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(leading_bytes >> 4) << 16) |
+           ((uint64_t)(stride_bytes >> 4) << 32) | (1ull << 46);
+}
+
+// 32-bit instruction descriptor for kind::tf32: D = fp32 (bits 4-5 = 1), A and B = tf32 (bits 7-9
+// and 10-12 = 2), both K-major (bits 15, 16 = 0), N >> 3 at bit 17, M >> 4 at bit 24
+__device__ __forceinline__ uint32_t instr_desc_tf32(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+
+// the mbarrier receives one arrival when every tcgen05.mma issued so far by this thread is done
+__device__ __forceinline__ void commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+
+__device__ __forceinline__ void ld_row8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Bounded wait for phase `parity` of an mbarrier: false when the limit ran out (the caller then
+// reports it and skips its output instead of spinning for ever).
+__device__ __forceinline__ bool wait_bounded(uint32_t mbar, uint32_t parity) {
+    for (int it = 0; it < (1 << 20); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(mbar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+}  // namespace umma
+
+constexpr int kTileRows = 128;  // points per block = rows of one tcgen05.mma
+
+template <int F, int LPS, bool HALF>
+__global__ void __launch_bounds__(kTileRows) forward_linear_kernel(const ForwardLinearArgs a) {
+    const Problem& p = a.p;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int chunks = a.k_pad / 4;                    // 16-byte column groups per row
+    const uint32_t stride_bytes = (uint32_t)chunks * 128u;  // between 8-row groups
+    unsigned char* tile_a = smem_raw;                  // [128 x k_pad] features
+    unsigned char* tile_b = smem_raw + (size_t)(kTileRows / 8) * stride_bytes;  // [H x k_pad] weight
+    __shared__ __align__(8) uint64_t mma_done;
+    __shared__ uint32_t tmem_base;
+
+    const int t = threadIdx.x;
+    const int warp = t >> 5;
+    const int H = a.out_features;
+    uint32_t tmem_cols = 32;  // allocation granularity: a power of two, at least 32 columns
+    while ((int)tmem_cols < H) tmem_cols <<= 1;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(umma::smem_u32(&tmem_base)),
+                     "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (t == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(umma::smem_u32(&mma_done)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+
+    // weight -> shared memory in the operand layout, rounded to tf32; columns beyond the row width are zero
+    for (int e = t; e < H * chunks; e += kTileRows) {
+        const int n = e / chunks, kc = e - n * chunks;
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* src = a.weight + (size_t)n * p.width + 4 * kc;
+        if (4 * kc + 0 < p.width) w.x = umma::to_tf32(__ldg(src + 0));
+        if (4 * kc + 1 < p.width) w.y = umma::to_tf32(__ldg(src + 1));
+        if (4 * kc + 2 < p.width) w.z = umma::to_tf32(__ldg(src + 2));
+        if (4 * kc + 3 < p.width) w.w = umma::to_tf32(__ldg(src + 3));
+        *reinterpret_cast<float4*>(tile_b + (size_t)(n >> 3) * stride_bytes + (size_t)kc * 128 + (n & 7) * 16) = w;
+    }
+
+    // this thread's point -> row t of the feature tile
+    const int64_t n_raw = (int64_t)blockIdx.x * kTileRows + t;
+    const bool active = n_raw < p.n_points;
+    const int64_t n = active ? n_raw : p.n_points - 1;  // idle rows shadow the last point and are not stored
+    float pos[D];
+    load_pos(p, n, pos);
+    unsigned char* row = tile_a + (size_t)(t >> 3) * stride_bytes + (t & 7) * 16;
+    const int lattice_cols = F * p.nr_levels;
+    // a column past the lattice levels: a concatenated raw coordinate (EncodingGPU.cuh:105-121) or padding
+    auto tail_value = [&](int c) -> float {
+        float v = 0.f;
+        const int i = c - lattice_cols;
+#pragma unroll
+        for (int j = 0; j < D; ++j) v = (i == j && c < p.width) ? pos[j] * p.points_scaling : v;
+        return v;
+    };
+    const int nsteps = (p.nr_levels + LPS - 1) / LPS;
+#pragma unroll 1
+    for (int s = 0; s < nsteps; ++s) {
+        float out[F * LPS];
+        encode_step<F, LPS, HALF>(p, pos, s * LPS, p.nr_levels, out);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = 8 * s + i;
+            out[i] = (c >= lattice_cols) ? tail_value(c) : out[i];
+        }
+        if (8 * s + 8 <= a.k_pad) {
+            *reinterpret_cast<float4*>(row + (size_t)(2 * s) * 128) =
+                make_float4(umma::to_tf32(out[0]), umma::to_tf32(out[1]), umma::to_tf32(out[2]), umma::to_tf32(out[3]));
+            *reinterpret_cast<float4*>(row + (size_t)(2 * s + 1) * 128) =
+                make_float4(umma::to_tf32(out[4]), umma::to_tf32(out[5]), umma::to_tf32(out[6]), umma::to_tf32(out[7]));
+        }
+    }
+    for (int kc = 2 * nsteps; kc < chunks; ++kc)
+        *reinterpret_cast<float4*>(row + (size_t)kc * 128) =
+            make_float4(umma::to_tf32(tail_value(4 * kc)), umma::to_tf32(tail_value(4 * kc + 1)),
+                        umma::to_tf32(tail_value(4 * kc + 2)), umma::to_tf32(tail_value(4 * kc + 3)));
+
+    // shared-memory writes of all threads -> visible to the tensor core (async proxy), then one thread issues
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_base;
+    if (t == 0) {
+        const uint32_t idesc = umma::instr_desc_tf32(kTileRows, H);
+        const uint32_t addr_a = umma::smem_u32(tile_a), addr_b = umma::smem_u32(tile_b);
+        for (int j = 0; j < a.k_pad / 8; ++j)  // one MMA consumes 8 columns = two 16-byte groups
+            umma::mma_tf32(tmem, umma::smem_desc(addr_a + (uint32_t)j * 256u, 128u, stride_bytes),
+                           umma::smem_desc(addr_b + (uint32_t)j * 256u, 128u, stride_bytes), idesc, j > 0);
+        umma::commit(umma::smem_u32(&mma_done));
+    }
+    // warp-uniform verdict: tcgen05.ld below must be executed by whole warps
+    const bool ok = __all_sync(kFullMask, umma::wait_bounded(umma::smem_u32(&mma_done), 0));
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!ok && a.status) atomicExch(a.status, 1);
+
+    // accumulator row t: tensor-memory lane 32*warp + lane, H consecutive columns
+    if (ok) {
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        float* dst = a.out + n_raw * H;
+        for (int c = 0; c < H; c += 8) {
+            float v[8];
+            umma::ld_row8(lane_base + (uint32_t)c, v);  // all 32 lanes of the warp take part
+            if (active) {
+                if (a.bias) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] += __ldg(a.bias + c + i);
+                }
+                reinterpret_cast<float4*>(dst + c)[0] = make_float4(v[0], v[1], v[2], v[3]);
+                reinterpret_cast<float4*>(dst + c)[1] = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------
@@ -719,6 +934,21 @@ cudaError_t launch_forward(const ForwardArgs& a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+template <int F, int LPS>
+cudaError_t launch_forward_linear(const ForwardLinearArgs& a, cudaStream_t st) {
+    const size_t smem = (size_t)(kTileRows + a.out_features) * a.k_pad * sizeof(float);
+    const dim3 g((unsigned)((a.p.n_points + kTileRows - 1) / kTileRows));
+    auto launch = [&](auto kernel) -> cudaError_t {
+        if (smem + 1024 > 48 * 1024) {  // the kernel's few static shared words count against the default limit
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
+        kernel<<<g, kTileRows, smem, st>>>(a);
+        return cudaGetLastError();
+    };
+    return a.p.table_half ? launch(forward_linear_kernel<F, LPS, true>) : launch(forward_linear_kernel<F, LPS, false>);
+}
+
 // The table is only read where something is gathered (position gradient, grad-grad features):
 // the scatter-only kernels have no fp16 variant.
 template <int F, int LPS>
@@ -771,6 +1001,15 @@ cudaError_t PERMUTO_CAT(launch_forward_dim, PERMUTO_DIM)(const ForwardArgs& a0, 
     const bool single = use_single_level(a0.p);
     const ForwardArgs a = with_schedule(a0, single, Traffic::Gather);
     PERMUTO_BY_WIDTH(launch_forward, a, single, st)
+}
+
+cudaError_t PERMUTO_CAT(launch_forward_linear_dim, PERMUTO_DIM)(const ForwardLinearArgs& a, cudaStream_t st) {
+    switch (a.p.nr_feat) {  // always whole 8-float steps: the tile is padded, not the level loop
+        case 2: return launch_forward_linear<2, 4>(a, st);
+        case 4: return launch_forward_linear<4, 2>(a, st);
+        case 8: return launch_forward_linear<8, 1>(a, st);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t PERMUTO_CAT(launch_backward_dim, PERMUTO_DIM)(const BackwardArgs& a0, cudaStream_t st) {

@@ -36,6 +36,17 @@ struct ForwardArgs {
     float* features;
 };
 
+// forward fused with the first linear layer of the consumer: out = features @ weight^T + bias
+struct ForwardLinearArgs {
+    Problem p;
+    const float* weight;   // [out_features, p.width] row-major (the layout of torch.nn.Linear.weight)
+    const float* bias;     // [out_features] or null
+    float* out;            // [N, out_features]
+    int32_t out_features;  // multiple of 16, 16..256
+    int32_t k_pad;         // p.width rounded up to a multiple of 8 (one tf32 MMA consumes 8)
+    int32_t* status;       // device word set non-zero when a wait on the tensor core ran out
+};
+
 struct BackwardArgs {
     Problem p;
     const float* grad_features;
@@ -71,6 +82,7 @@ int sm_count();
 // Defined once per pos_dim in permuto_dim.cu (compiled with -DPERMUTO_DIM=d).
 #define PERMUTO_DECLARE_DIM(d)                                                        \
     cudaError_t launch_forward_dim##d(const ForwardArgs&, cudaStream_t);              \
+    cudaError_t launch_forward_linear_dim##d(const ForwardLinearArgs&, cudaStream_t); \
     cudaError_t launch_backward_dim##d(const BackwardArgs&, cudaStream_t);            \
     cudaError_t launch_double_backward_dim##d(const DoubleBackwardArgs&, cudaStream_t); \
     cudaError_t launch_debug_dim##d(const DebugArgs&, cudaStream_t);

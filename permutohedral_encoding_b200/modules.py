@@ -137,6 +137,23 @@ class PermutoEncoding(torch.nn.Module):
             self._half_ptr = v.data_ptr()
         return self._half
 
+    @torch.no_grad()
+    def forward_linear(self, positions, linear, anneal_window=None, status=None):
+        """Inference shortcut for ``linear(self(positions))`` where ``linear`` is the
+        ``torch.nn.Linear`` (or a ``(weight, bias)`` pair) that consumes the features: one kernel,
+        the ``[N, output_dims()]`` features stay on chip and the product runs on the tensor cores
+        (operands rounded to tf32, fp32 accumulation -- about 1e-3 relative to the magnitude of
+        the summed terms).  No gradients are recorded; train through ``forward``."""
+        if anneal_window is None:
+            anneal_window = self.anneal_window
+        if anneal_window.device != positions.device:
+            anneal_window = anneal_window.to(positions.device)
+        self.fixed_params.m_random_shift_per_level = self.random_shift_per_level
+        weight, bias = (linear.weight, linear.bias) if hasattr(linear, "weight") else linear
+        half = self._half_copy() if getattr(self, "half_precision_table", False) else None
+        inp = _C.EncodingInput(self.lattice_values, positions, anneal_window, False, False, half)
+        return self.lattice.forward_linear(inp, weight, bias, status)
+
     def output_dims(self):
         nr_resolutions_extra = 0
         if self.concat_points:

@@ -69,7 +69,8 @@ class LatticeAdamW(torch.optim.Optimizer):
                     state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
                 state["step"] += 1
                 grad = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
-                adam_step(p.data, grad, state["exp_avg"], state["exp_avg_sq"], state["step"], group["lr"],
+                # the parameter itself, not p.data: the step must bump ITS version counter
+                adam_step(p, grad, state["exp_avg"], state["exp_avg_sq"], state["step"], group["lr"],
                           group["betas"], group["eps"], group["weight_decay"], group["skip_untouched"],
                           group["zero_grad_in_step"] and grad is p.grad)
         return loss

@@ -92,14 +92,14 @@ def test_training_loop_with_the_fused_step_reduces_the_loss():
     from permutohedral_encoding_b200.optim import LatticeAdamW
     torch.manual_seed(0)
     m = PermutoEncoding(3, 2 ** 14, 8, 2, np.geomspace(1.0, 1e-2, 8))
-    opt = LatticeAdamW([m.lattice_values], lr=1e-1, betas=(0.9, 0.99), eps=1e-15, weight_decay=0.0,
+    opt = LatticeAdamW([m.lattice_values], lr=2e-1, betas=(0.9, 0.99), eps=1e-15, weight_decay=0.0,
                        skip_untouched=True)
     pts = torch.rand(5000, 3, device=DEV) - 0.5
     losses = []
-    for _ in range(30):
+    for _ in range(100):
         loss = ((m(pts) - 10) ** 2).mean()
         opt.zero_grad()
         loss.backward()
         opt.step()
         losses.append(loss.item())
-    assert losses[-1] < 0.5 * losses[0]
+    assert losses[-1] < 0.1 * losses[0], (losses[0], losses[-1])
