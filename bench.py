@@ -21,6 +21,8 @@ same way in both arms (``--impl ours`` and ``--impl reference``):
   dim4, dim6            pos_dim 4 / 6, 16 levels, capacity 2^20, 2^20 points, forward + backward
   train_with_optimizer  the train step with MSE loss and an AdamW step on the table
                         (the reference's examples/performance.py loop)
+  forward_linear        inference of the train workload followed by Linear(48, 32), the first layer
+                        of the reference's toy MLP; this repo runs it as one fused kernel
 
 Rank 0 prints ONE JSON line.  ``value`` is whole-job Mpoints/s with inputs resident in HBM,
 timed on the device with CUDA events (max over ranks, median over repeats of K steps);
@@ -60,7 +62,13 @@ def parse_args():
     ap.add_argument("--copy-out", action="store_true", help="copy the reduced gradient out of the symmetric buffer")
     ap.add_argument("--clear", default="inline", choices=["inline", "early"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-blocks", action="store_true", help="skip the per-configuration blocks at N = 1")
+    ap.add_argument("--blocks", default=None,
+                    help="comma-separated per-configuration blocks to add at N = 1 (train, forward_linear, "
+                         "train_with_optimizer, readme_forward, eikonal, dim4, dim6); default: all of them for the "
+                         "sharded workload, none otherwise")
+    ap.add_argument("--no-blocks", action="store_true", help="same as --blocks ''")
+    ap.add_argument("--total-points", type=int, default=None,
+                    help="override the workload's points per step (small cases for profiler captures)")
     ap.add_argument("--min-timed-seconds", type=float, default=0.5)
     return ap.parse_args()
 
@@ -485,6 +493,41 @@ def block_optimizer(impl, runner, pos, device, steps):
                     "(betas 0.9/0.99, eps 1e-15, no weight decay), as in the reference's examples/performance.py"}
 
 
+def block_forward_linear(impl, runner, pos, device, steps):
+    """Inference of the encoding followed by the consumer's first layer, Linear(48, 32) as in the
+    reference's examples/train_toy_example.py:18-19, on the train workload.  Ours: one fused kernel
+    (features never written; tensor cores) and, beside it, the unfused pair; reference: its module
+    followed by the same torch layer."""
+    gen = torch.Generator(device="cpu").manual_seed(77)
+    width = runner.encode(pos[:8]).shape[1]
+    lin = torch.nn.Linear(width, 32)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn((32, width), generator=gen) / width ** 0.5)
+        lin.bias.copy_(torch.randn(32, generator=gen) * 0.1)
+    lin = lin.to(device)
+    n = pos.shape[0]
+    with torch.no_grad():
+        ms_pair, reps = timed(lambda: lin(runner.encode(pos)), steps, 3, device, 0.2, local_sync)
+        blk = {"unit": "Mpoints/s", "out_features": 32,
+               "what": "train workload, inference: encoding followed by torch.nn.Linear(48, 32)"}
+        if impl == "ours":
+            ms_fused, reps = timed(lambda: runner.m.forward_linear(pos, lin), steps, 3, device, 0.2, local_sync)
+            d, L = 3, WORKLOADS["train"]["nr_levels"]
+            alg = n * (4 * d + 4 * L * (d + 1) * 2 + 4 * 32)   # positions, gathered entries, [N, 32] output
+            blk.update({"value": round(n / ms_fused / 1e3, 2), "ms_per_step": round(ms_fused, 4), "repeats": reps,
+                        "unfused": {"value": round(n / ms_pair / 1e3, 2), "ms_per_step": round(ms_pair, 4),
+                                    "what": "module forward, then the torch layer"},
+                        "hbm_bytes_per_point": {"fused": 4 * d + 4 * 32, "unfused": 4 * d + 4 * width * 2 + 4 * 32},
+                        "roofline": {"bound": "hbm", "achieved": round(alg / (ms_fused * 1e-3) / 1e9, 1), "peak": HBM_PEAK,
+                                     "unit": "GB/s", "frac": round(alg / (ms_fused * 1e-3) / 1e9 / HBM_PEAK, 4),
+                                     "algorithmic_bytes_per_launch": alg,
+                                     "note": "bound by the rate of random table gathers, like the plain forward; the "
+                                             "tensor-core product (2*48*32 flop per point) is negligible"}})
+        else:
+            blk.update({"value": round(n / ms_pair / 1e3, 2), "ms_per_step": round(ms_pair, 4), "repeats": reps})
+    return blk
+
+
 def allreduce_check(runner, pos, grad_out, device):
     """Outside the timed region: the gradient the overlapped, bucketed all-reduce left in .grad
     against a plain all-reduce of an un-hooked local backward.  Largest error relative to the
@@ -524,8 +567,20 @@ def reference_cpu_line(name, w):
 def main():
     args = ARGS
     name = args.workload
-    w = WORKLOADS[name]
+    w = dict(WORKLOADS[name])
+    if args.total_points:
+        w["total_points"] = int(args.total_points)
     d, L = w["pos_dim"], w["nr_levels"]
+    all_blocks = ["train", "forward_linear", "train_with_optimizer", "readme_forward", "eikonal", "dim4", "dim6"]
+    if args.no_blocks or WORLD > 1:
+        blocks = []
+    elif args.blocks is not None:
+        blocks = [b for b in args.blocks.split(",") if b]
+        unknown = [b for b in blocks if b not in all_blocks]
+        if unknown:
+            raise SystemExit(f"unknown block(s) {unknown}; choose from {all_blocks}")
+    else:
+        blocks = all_blocks if (name == "sharded" and not args.total_points) else []
     if args.impl == "reference" and w.get("nr_feat", 2) != 2:
         if RANK == 0:
             print(json.dumps({"impl": "reference", "unavailable": "the reference implements nr_feat_per_level == 2 only"}))
@@ -610,20 +665,28 @@ def main():
         if WORLD > 1:
             line["allreduce_check"] = allreduce_check(runner, pos, grad_out, device)
 
-    if WORLD == 1 and not args.no_blocks and name == "sharded":
+    if blocks:
         del runner, pos, grad_out, feeder
         torch.cuda.empty_cache()
         ceil2 = ceilings if args.impl == "ours" else None
-        blk, r2, p2 = block_train(args.impl, "train", device, args.steps, ceil2)
-        line["train"] = blk
-        line["train_with_optimizer"] = block_optimizer(args.impl, r2, p2, device, args.steps)
-        del r2, p2
-        line["readme_forward"] = block_readme_forward(args.impl, device)
-        line["eikonal"] = block_eikonal(args.impl, device, args.steps)
+        if {"train", "forward_linear", "train_with_optimizer"} & set(blocks):
+            blk, r2, p2 = block_train(args.impl, "train", device, args.steps, ceil2)
+            if "train" in blocks:
+                line["train"] = blk
+            if "forward_linear" in blocks:
+                line["forward_linear"] = block_forward_linear(args.impl, r2, p2, device, args.steps)
+            if "train_with_optimizer" in blocks:
+                line["train_with_optimizer"] = block_optimizer(args.impl, r2, p2, device, args.steps)
+            del r2, p2
+        if "readme_forward" in blocks:
+            line["readme_forward"] = block_readme_forward(args.impl, device)
+        if "eikonal" in blocks:
+            line["eikonal"] = block_eikonal(args.impl, device, args.steps)
         for nm in ("dim4", "dim6"):
-            torch.cuda.empty_cache()
-            line[nm], r3, p3 = block_train(args.impl, nm, device, args.steps, None)
-            del r3, p3
+            if nm in blocks:
+                torch.cuda.empty_cache()
+                line[nm], r3, p3 = block_train(args.impl, nm, device, args.steps, None)
+                del r3, p3
     if args.impl == "ours" and RANK == 0 and WORLD == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(w)
     if WORLD > 1:

@@ -94,7 +94,10 @@ typedef struct permuto_inputs {
 enum {
     PERMUTO_ZERO_OUTPUTS = 1,      /* clear lattice_grad (the selected levels) and positions_grad before accumulating */
     PERMUTO_NO_AGGREGATE = 2,      /* do not merge colliding scatter-adds inside a warp before the atomics            */
-    PERMUTO_KEEP_POSITIONS_GRAD = 4 /* with ZERO_OUTPUTS: leave positions_grad as it is (a later bucket of levels)     */
+    PERMUTO_KEEP_POSITIONS_GRAD = 4, /* with ZERO_OUTPUTS: leave positions_grad as it is (a later bucket of levels)    */
+    PERMUTO_CONCAT_POSITIONS_GRAD = 8 /* backward, concat_points: also add points_scaling * grad of the concatenated
+                                         coordinates to positions_grad.  Off by default because the reference omits
+                                         this term (src/Encoding.cu:129-134: its backward skips the extra levels)   */
 };
 
 int permuto_abi_version(void);

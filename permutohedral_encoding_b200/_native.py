@@ -34,6 +34,7 @@ PERMUTO_ERR_CUDA = -3
 PERMUTO_ZERO_OUTPUTS = 1
 PERMUTO_NO_AGGREGATE = 2
 PERMUTO_KEEP_POSITIONS_GRAD = 4
+PERMUTO_CONCAT_POSITIONS_GRAD = 8
 PERMUTO_ADAM_SKIP_UNTOUCHED = 1
 PERMUTO_ADAM_ZERO_GRAD = 2
 
@@ -220,6 +221,9 @@ class EncodingWrapper:
             raise RuntimeError("Encoding: nr_feat_per_level must be 2, 4 or 8")
         self.fixed = fixed_params
         self.aggregate_collisions = True
+        # The reference gives the positions no gradient through the concatenated raw points
+        # (its backward skips those columns); True adds that term.
+        self.concat_positions_grad = False
         self.backward_hook = None          # set by distributed.LatticeGradAllReduce
         self.double_backward_hook = None
         self._feat = int(nr_feat_per_level)
@@ -294,6 +298,8 @@ class EncodingWrapper:
         f = PERMUTO_ZERO_OUTPUTS if zero else 0
         if not self.aggregate_collisions:
             f |= PERMUTO_NO_AGGREGATE
+        if self.concat_positions_grad:
+            f |= PERMUTO_CONCAT_POSITIONS_GRAD
         return f
 
     # -- the three operations -------------------------------------------------------------------

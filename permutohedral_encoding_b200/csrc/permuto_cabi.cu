@@ -187,6 +187,7 @@ int permuto_forward_linear(const permuto_config* cfg, const permuto_inputs* in, 
     a.out_features = out_features;
     a.k_pad = (a.p.width + 7) / 8 * 8;
     a.status = status;
+    a.out_vec8_ok = aligned(out, 32) ? 1 : 0;
     cudaError_t err;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     PERMUTO_DISPATCH(launch_forward_linear, a, st)
@@ -214,6 +215,7 @@ int permuto_backward(const permuto_config* cfg, const permuto_inputs* in, const 
     a.lattice_grad = lattice_grad;
     a.positions_grad = positions_grad;
     a.aggregate = (flags & PERMUTO_NO_AGGREGATE) ? 0 : 1;
+    a.concat_grad = (flags & PERMUTO_CONCAT_POSITIONS_GRAD) ? 1 : 0;
     a.p.rows_vec8_ok = rows_vec8(a.p, grad_features, nullptr);
     if (flags & PERMUTO_ZERO_OUTPUTS) {
         cudaError_t e = cudaSuccess;

@@ -305,16 +305,16 @@ __global__ void __launch_bounds__(kThreads, (F == 2 ? PERMUTO_MIN_BLOCKS_FORWARD
 // ------------------------------------------------------------------------------------------
 // The users of the encoding feed the [N, F*L] feature row straight into a small MLP (reference:
 // examples/train_toy_example.py:18-26, README.md:39-40).  Here a block of 128 threads encodes 128
-// points, keeps the 128 x K feature tile in shared memory (K = F*(L+extra), rounded to tf32) and
-// multiplies it by the layer's weight [H, K] on the tensor cores: K/8 tcgen05.mma of shape
-// 128 x H x 8 (kind::tf32, fp32 accumulate) issued by one thread, accumulator in tensor memory,
-// read back with tcgen05.ld (thread t holds row t) and written as [N, H] with the bias added.
-// The 192 B/point feature row and the separate GEMM's read of it never touch HBM.
+// points, passes the 128 x K feature tile (K = F*(L+extra), rounded to tf32) through shared memory
+// 8 columns at a time and multiplies it by the layer's weight [H, K] on the tensor cores: K/8
+// tcgen05.mma of shape 128 x H x 8 (kind::tf32, fp32 accumulate) issued by one thread, accumulator
+// in tensor memory, read back with tcgen05.ld (thread t holds row t) and written as [N, H] with
+// the bias added.  The 192 B/point feature row and the separate GEMM's read of it never touch HBM.
 //
 // Shared-memory operand layout (K-major, no swizzle -- the canonical layout of the tcgen05
 // matrix descriptor): 8 rows x 16 bytes form a contiguous 128-byte core matrix; the core
 // matrices of consecutive 4-column groups follow each other (leading byte offset 128) and those
-// of consecutive 8-row groups are K/4 * 128 bytes apart (stride byte offset).
+// of consecutive 8-row groups are a fixed number of bytes apart (stride byte offset).
 namespace umma {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -354,16 +354,6 @@ __device__ __forceinline__ void commit(uint32_t mbar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
 }
 
-__device__ __forceinline__ void ld_row8(uint32_t taddr, float (&v)[8]) {
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // Bounded wait for phase `parity` of an mbarrier: false when the limit ran out (the caller then
 // reports it and skips its output instead of spinning for ever).
 __device__ __forceinline__ bool wait_bounded(uint32_t mbar, uint32_t parity) {
@@ -386,16 +376,29 @@ __device__ __forceinline__ bool wait_bounded(uint32_t mbar, uint32_t parity) {
 }  // namespace umma
 
 constexpr int kTileRows = 128;  // points per block = rows of one tcgen05.mma
+#ifndef PERMUTO_FUSED_RING
+#define PERMUTO_FUSED_RING 2
+#endif
+constexpr int kRing = PERMUTO_FUSED_RING;  // 128 x 8 feature slices in flight between the encoder and the tensor core
+constexpr uint32_t kSliceBytes = kTileRows * 8 * 4;  // one slice: 128 rows x 8 tf32 = 4 KB
 
+// The feature tile is never whole in shared memory: every step of 8 columns is one K = 8 slice of
+// the product, written into a ring of kRing slices and consumed by one tcgen05.mma right away
+// (accumulating in tensor memory).  That keeps the block at 8 KB + the weight instead of
+// 128 x K x 4 bytes, so that shared memory neither limits the resident blocks nor eats the L1
+// capacity the coarse levels' gathers live on.
+#ifndef PERMUTO_FUSED_MIN_BLOCKS
+#define PERMUTO_FUSED_MIN_BLOCKS 8
+#endif
 template <int F, int LPS, bool HALF>
-__global__ void __launch_bounds__(kTileRows) forward_linear_kernel(const ForwardLinearArgs a) {
+__global__ void __launch_bounds__(kTileRows, (F == 2 ? PERMUTO_FUSED_MIN_BLOCKS : 4)) forward_linear_kernel(const ForwardLinearArgs a) {
     const Problem& p = a.p;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int chunks = a.k_pad / 4;                    // 16-byte column groups per row
-    const uint32_t stride_bytes = (uint32_t)chunks * 128u;  // between 8-row groups
-    unsigned char* tile_a = smem_raw;                  // [128 x k_pad] features
-    unsigned char* tile_b = smem_raw + (size_t)(kTileRows / 8) * stride_bytes;  // [H x k_pad] weight
-    __shared__ __align__(8) uint64_t mma_done;
+    const int chunks = a.k_pad / 4;                         // 16-byte column groups per weight row
+    const uint32_t b_stride = (uint32_t)chunks * 128u;      // weight: between 8-row groups
+    unsigned char* ring = smem_raw;                         // kRing slices of [128 x 8]
+    unsigned char* tile_b = smem_raw + kRing * kSliceBytes; // [H x k_pad] weight
+    __shared__ __align__(8) uint64_t slice_free[kRing];     // arrives when the MMA that read the slice is done
     __shared__ uint32_t tmem_base;
 
     const int t = threadIdx.x;
@@ -411,29 +414,44 @@ __global__ void __launch_bounds__(kTileRows) forward_linear_kernel(const Forward
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (t == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(umma::smem_u32(&mma_done)) : "memory");
+#pragma unroll
+        for (int i = 0; i < kRing; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(umma::smem_u32(&slice_free[i])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 
     // weight -> shared memory in the operand layout, rounded to tf32; columns beyond the row width are zero
+    const bool w_vec = (p.width % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.weight) & 15u) == 0);
     for (int e = t; e < H * chunks; e += kTileRows) {
         const int n = e / chunks, kc = e - n * chunks;
         float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* src = a.weight + (size_t)n * p.width + 4 * kc;
-        if (4 * kc + 0 < p.width) w.x = umma::to_tf32(__ldg(src + 0));
-        if (4 * kc + 1 < p.width) w.y = umma::to_tf32(__ldg(src + 1));
-        if (4 * kc + 2 < p.width) w.z = umma::to_tf32(__ldg(src + 2));
-        if (4 * kc + 3 < p.width) w.w = umma::to_tf32(__ldg(src + 3));
-        *reinterpret_cast<float4*>(tile_b + (size_t)(n >> 3) * stride_bytes + (size_t)kc * 128 + (n & 7) * 16) = w;
+        if (w_vec && 4 * kc + 3 < p.width) {
+            w = __ldg(reinterpret_cast<const float4*>(src));
+        } else {
+            if (4 * kc + 0 < p.width) w.x = __ldg(src + 0);
+            if (4 * kc + 1 < p.width) w.y = __ldg(src + 1);
+            if (4 * kc + 2 < p.width) w.z = __ldg(src + 2);
+            if (4 * kc + 3 < p.width) w.w = __ldg(src + 3);
+        }
+        *reinterpret_cast<float4*>(tile_b + (size_t)(n >> 3) * b_stride + (size_t)kc * 128 + (n & 7) * 16) =
+            make_float4(umma::to_tf32(w.x), umma::to_tf32(w.y), umma::to_tf32(w.z), umma::to_tf32(w.w));
     }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_base;
+    const uint32_t idesc = umma::instr_desc_tf32(kTileRows, H);
+    const uint32_t addr_ring = umma::smem_u32(ring), addr_b = umma::smem_u32(tile_b);
 
-    // this thread's point -> row t of the feature tile
+    // this thread's point -> row t of every slice
     const int64_t n_raw = (int64_t)blockIdx.x * kTileRows + t;
     const bool active = n_raw < p.n_points;
     const int64_t n = active ? n_raw : p.n_points - 1;  // idle rows shadow the last point and are not stored
     float pos[D];
     load_pos(p, n, pos);
-    unsigned char* row = tile_a + (size_t)(t >> 3) * stride_bytes + (t & 7) * 16;
+    const uint32_t row_off = (uint32_t)(t >> 3) * 256u + (uint32_t)(t & 7) * 16u;  // 8-row groups 256 bytes apart
     const int lattice_cols = F * p.nr_levels;
     // a column past the lattice levels: a concatenated raw coordinate (EncodingGPU.cuh:105-121) or padding
     auto tail_value = [&](int c) -> float {
@@ -443,61 +461,72 @@ __global__ void __launch_bounds__(kTileRows) forward_linear_kernel(const Forward
         for (int j = 0; j < D; ++j) v = (i == j && c < p.width) ? pos[j] * p.points_scaling : v;
         return v;
     };
-    const int nsteps = (p.nr_levels + LPS - 1) / LPS;
+    const int nsteps = (p.nr_levels + LPS - 1) / LPS;  // steps that hold lattice levels
+    const int ksteps = a.k_pad / 8;                    // all steps: one tcgen05.mma each
+    bool ok = true;
 #pragma unroll 1
-    for (int s = 0; s < nsteps; ++s) {
-        float out[F * LPS];
-        encode_step<F, LPS, HALF>(p, pos, s * LPS, p.nr_levels, out);
+    for (int s = 0; s < ksteps; ++s) {
+        float out[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int c = 8 * s + i;
-            out[i] = (c >= lattice_cols) ? tail_value(c) : out[i];
+        for (int i = 0; i < 8; ++i) out[i] = 0.f;
+        if (s < nsteps) encode_step<F, LPS, HALF>(p, pos, s * LPS, p.nr_levels, out);
+        if (8 * s + 8 > lattice_cols) {  // block-uniform: only the last step(s) reach past the lattice levels
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = 8 * s + i;
+                out[i] = (c >= lattice_cols) ? tail_value(c) : out[i];
+            }
         }
-        if (8 * s + 8 <= a.k_pad) {
-            *reinterpret_cast<float4*>(row + (size_t)(2 * s) * 128) =
-                make_float4(umma::to_tf32(out[0]), umma::to_tf32(out[1]), umma::to_tf32(out[2]), umma::to_tf32(out[3]));
-            *reinterpret_cast<float4*>(row + (size_t)(2 * s + 1) * 128) =
-                make_float4(umma::to_tf32(out[4]), umma::to_tf32(out[5]), umma::to_tf32(out[6]), umma::to_tf32(out[7]));
+        const int slot = s % kRing;
+        // the MMA that read this slice kRing steps ago must be done before it is overwritten
+        if (s >= kRing) ok = umma::wait_bounded(umma::smem_u32(&slice_free[slot]), (uint32_t)((s / kRing - 1) & 1)) && ok;
+        unsigned char* dst = ring + (size_t)slot * kSliceBytes + row_off;
+        *reinterpret_cast<float4*>(dst) =
+            make_float4(umma::to_tf32(out[0]), umma::to_tf32(out[1]), umma::to_tf32(out[2]), umma::to_tf32(out[3]));
+        *reinterpret_cast<float4*>(dst + 128) =
+            make_float4(umma::to_tf32(out[4]), umma::to_tf32(out[5]), umma::to_tf32(out[6]), umma::to_tf32(out[7]));
+        // the block's writes -> visible to the tensor core (async proxy); then one thread issues the slice's MMA
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (t == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            umma::mma_tf32(tmem, umma::smem_desc(addr_ring + (uint32_t)slot * kSliceBytes, 128u, 256u),
+                           umma::smem_desc(addr_b + (uint32_t)s * 256u, 128u, b_stride), idesc, s > 0);
+            umma::commit(umma::smem_u32(&slice_free[slot]));  // covers every MMA issued so far
         }
     }
-    for (int kc = 2 * nsteps; kc < chunks; ++kc)
-        *reinterpret_cast<float4*>(row + (size_t)kc * 128) =
-            make_float4(umma::to_tf32(tail_value(4 * kc)), umma::to_tf32(tail_value(4 * kc + 1)),
-                        umma::to_tf32(tail_value(4 * kc + 2)), umma::to_tf32(tail_value(4 * kc + 3)));
-
-    // shared-memory writes of all threads -> visible to the tensor core (async proxy), then one thread issues
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    // the last commit covers the whole product
+    const int last = ksteps - 1;
+    ok = umma::wait_bounded(umma::smem_u32(&slice_free[last % kRing]), (uint32_t)((last / kRing) & 1)) && ok;
+    ok = __syncthreads_and(ok) != 0;  // block-uniform verdict: tcgen05.ld below must be executed by whole warps
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = tmem_base;
-    if (t == 0) {
-        const uint32_t idesc = umma::instr_desc_tf32(kTileRows, H);
-        const uint32_t addr_a = umma::smem_u32(tile_a), addr_b = umma::smem_u32(tile_b);
-        for (int j = 0; j < a.k_pad / 8; ++j)  // one MMA consumes 8 columns = two 16-byte groups
-            umma::mma_tf32(tmem, umma::smem_desc(addr_a + (uint32_t)j * 256u, 128u, stride_bytes),
-                           umma::smem_desc(addr_b + (uint32_t)j * 256u, 128u, stride_bytes), idesc, j > 0);
-        umma::commit(umma::smem_u32(&mma_done));
-    }
-    // warp-uniform verdict: tcgen05.ld below must be executed by whole warps
-    const bool ok = __all_sync(kFullMask, umma::wait_bounded(umma::smem_u32(&mma_done), 0));
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (!ok && a.status) atomicExch(a.status, 1);
+    if (!ok && a.status && t == 0) atomicExch(a.status, 1);
 
-    // accumulator row t: tensor-memory lane 32*warp + lane, H consecutive columns
+    // accumulator row t: tensor-memory lane 32*warp + lane, H consecutive columns, 16 at a time
     if (ok) {
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
         float* dst = a.out + n_raw * H;
-        for (int c = 0; c < H; c += 8) {
-            float v[8];
-            umma::ld_row8(lane_base + (uint32_t)c, v);  // all 32 lanes of the warp take part
+        for (int c = 0; c < H; c += 16) {
+            uint32_t r[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(lane_base + (uint32_t)c));  // all 32 lanes of the warp take part
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if (active) {
-                if (a.bias) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] += __ldg(a.bias + c + i);
+                for (int h = 0; h < 2; ++h) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * h + i]) + (a.bias ? __ldg(a.bias + c + 8 * h + i) : 0.f);
+                    if (a.out_vec8_ok) {
+                        store8(dst + c + 8 * h, v);
+                    } else {
+                        reinterpret_cast<float4*>(dst + c + 8 * h)[0] = make_float4(v[0], v[1], v[2], v[3]);
+                        reinterpret_cast<float4*>(dst + c + 8 * h)[1] = make_float4(v[4], v[5], v[6], v[7]);
+                    }
                 }
-                reinterpret_cast<float4*>(dst + c)[0] = make_float4(v[0], v[1], v[2], v[3]);
-                reinterpret_cast<float4*>(dst + c)[1] = make_float4(v[4], v[5], v[6], v[7]);
             }
         }
     }
@@ -728,6 +757,14 @@ backward_kernel(const BackwardArgs a) {
             }
         }
     }
+    // Optional: the concatenated raw coordinates are outputs too, d out[F*L + i] / d pos[i] =
+    // points_scaling.  The reference leaves this term out (its backward grids exclude the extra
+    // levels, src/Encoding.cu:129-134,161), so it is added only on request.
+    if (POS && a.concat_grad && p.extra_levels > 0 && blockIdx.y == 0 && p.level_begin == 0) {
+        const float* g = a.grad_features + n * p.width + F * p.nr_levels;
+#pragma unroll
+        for (int i = 0; i < D; ++i) dpos[i] = fmaf(__ldg(g + i), p.points_scaling, dpos[i]);
+    }
     if (POS && active) {
         float* dst = a.positions_grad + n * D;
 #pragma unroll
@@ -936,7 +973,7 @@ cudaError_t launch_forward(const ForwardArgs& a, cudaStream_t st) {
 
 template <int F, int LPS>
 cudaError_t launch_forward_linear(const ForwardLinearArgs& a, cudaStream_t st) {
-    const size_t smem = (size_t)(kTileRows + a.out_features) * a.k_pad * sizeof(float);
+    const size_t smem = (size_t)kRing * kSliceBytes + (size_t)a.out_features * a.k_pad * sizeof(float);
     const dim3 g((unsigned)((a.p.n_points + kTileRows - 1) / kTileRows));
     auto launch = [&](auto kernel) -> cudaError_t {
         if (smem + 1024 > 48 * 1024) {  // the kernel's few static shared words count against the default limit

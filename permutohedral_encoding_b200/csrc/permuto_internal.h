@@ -45,6 +45,7 @@ struct ForwardLinearArgs {
     int32_t out_features;  // multiple of 16, 16..256
     int32_t k_pad;         // p.width rounded up to a multiple of 8 (one tf32 MMA consumes 8)
     int32_t* status;       // device word set non-zero when a wait on the tensor core ran out
+    int32_t out_vec8_ok;   // out is 32-byte aligned (rows are multiples of 64 bytes): 256-bit stores
 };
 
 struct BackwardArgs {
@@ -53,6 +54,7 @@ struct BackwardArgs {
     float* lattice_grad;    // may be null
     float* positions_grad;  // may be null
     int32_t aggregate;      // merge colliding scatter-adds inside a warp
+    int32_t concat_grad;    // add the gradient that reaches the positions through the concatenated raw points
 };
 
 struct DoubleBackwardArgs {

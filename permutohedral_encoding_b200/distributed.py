@@ -78,8 +78,9 @@ class LatticeGradAllReduce:
     With the symmetric-memory path the gradient handed to autograd is a *view* of one of two
     persistent communication buffers used alternately (``copy_out=False``, the default): no
     per-step allocation and no 100 MB copy out of the buffer.  The tensor stays valid until the
-    backward after the next one; a caller that keeps a gradient longer clones it or passes
-    ``copy_out=True``.  Gradient accumulation works: a buffer that the parameter's ``.grad``
+    backward after the next one (with ``clear="early"``: until the next backward starts, because
+    that is when the other buffer is cleared); a caller that keeps a gradient longer clones it or
+    passes ``copy_out=True``.  Gradient accumulation works: a buffer that the parameter's ``.grad``
     still aliases is never the one written.
 
     Constructing the hook is a collective call when ``multimem`` is not False: every rank of the
@@ -259,8 +260,6 @@ class LatticeGradAllReduce:
                         torch.mul(lv[l0:l1], scale, out=out[l0:l1])
                 elif scale is not None:
                     lv[l0:l1].mul_(scale)
-        if not inline_clear:
-            self._precleared = -1 if not early_next else self._precleared
         done = torch.cuda.Event()
         done.record(comm)
         current.wait_event(done)

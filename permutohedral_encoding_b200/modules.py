@@ -26,6 +26,9 @@ class PermutoEncoding(torch.nn.Module):
     access moves a 32-byte sector whatever it uses of it, and a random access costs about the same
     whether it moves 8 or 16 bytes, so e.g. 12 levels of 4 features produce 48 outputs in 60 % of
     the time of 24 x 2.
+    ``concat_points_grad=True`` completes the position gradient of ``concat_points``: the
+    reference (and the default here) gives the positions no gradient through the concatenated raw
+    coordinates, because its backward skips those columns (src/Encoding.cu:129-134).
     ``half_precision_table=True`` (not in the reference, which only hints at it,
     kernels/permutohedral_encoding/EncodingGPU.cuh:12) makes the kernels gather from an fp16 copy
     of ``lattice_values``: storage only -- products, sums, outputs, the parameter, its gradient
@@ -35,8 +38,9 @@ class PermutoEncoding(torch.nn.Module):
 
     def __init__(self, pos_dim, capacity, nr_levels, nr_feat_per_level, scale_per_level,
                  appply_random_shift_per_level=True, concat_points=False, concat_points_scaling=1.0,
-                 half_precision_table=False):
+                 half_precision_table=False, concat_points_grad=False):
         super().__init__()
+        self.concat_points_grad = bool(concat_points_grad)
         self.half_precision_table = bool(half_precision_table)
         self._half, self._half_version, self._half_ptr = None, -1, 0
         self.pos_dim = pos_dim
@@ -66,6 +70,7 @@ class PermutoEncoding(torch.nn.Module):
                                               self.scale_per_level, self.random_shift_per_level, self.concat_points,
                                               self.concat_points_scaling)
         lattice = _C.EncodingWrapper.create(self.pos_dim, self.nr_feat_per_level, fixed_params)
+        lattice.concat_positions_grad = bool(getattr(self, "concat_points_grad", False))
         return fixed_params, lattice
 
     def __getstate__(self):

@@ -663,3 +663,29 @@ def test_half_precision_table_module(nat, oracle):
     m2 = pickle.loads(pickle.dumps(m))
     with torch.no_grad():
         assert torch.equal(m2(pos), out2)
+
+
+def test_concat_points_position_gradient_on_request(nat, oracle):
+    """By default the positions get no gradient through the concatenated raw coordinates (the
+    reference's behaviour, pinned by the concat fixture); with the switch on, exactly
+    points_scaling * upstream gradient of those columns is added."""
+    name = "concat_d3"
+    c, inp = cases.CASES[name], cases.make_inputs(name)
+    enc, fx = make_encoding(nat, c, inp)
+    table, pos, anneal, go = T(inp["table"]), T(inp["positions"]), T(inp["anneal"]), T(inp["grad_out"])
+    I = nat.EncodingInput(table, pos, anneal, False, True)
+    _, pg_ref = enc.backward(I, go)
+    enc.concat_positions_grad = True
+    _, pg_full = enc.backward(I, go)
+    base = 2 * c["nr_levels"]
+    extra = go[:, base:base + 3] * c.get("points_scaling", 1.0)
+    assert torch.allclose(pg_full - pg_ref, extra, rtol=1e-5, atol=1e-5 * float(pg_ref.abs().max()))
+    from permutohedral_encoding_b200 import PermutoEncoding
+    m = PermutoEncoding(3, c["capacity"], c["nr_levels"], 2, inp["sigmas"], concat_points=True,
+                        concat_points_scaling=c.get("points_scaling", 1.0), concat_points_grad=True)
+    with torch.no_grad():
+        m.lattice_values.copy_(table)
+        m.random_shift_per_level.copy_(T(inp["shift"]))
+    x = pos.clone().requires_grad_(True)
+    m(x, anneal).backward(go)
+    assert torch.allclose(x.grad, pg_full, rtol=1e-4, atol=1e-4 * float(pg_full.abs().max()))
