@@ -9,8 +9,10 @@
 // access (ld/st.global.v8.f32, new on sm_100), directly in the final [N, F*L] layout -- no
 // transposed intermediate.  F = 2 is the reference's only supported width; F = 4 and 8 (which
 // the reference lists as not yet implemented, Encoding.cuh:140-143) make every table access a
-// 16- or 32-byte one, i.e. half or all of the sector the memory system moves anyway (a 16-byte
-// random access runs at the rate of an 8-byte one, a 32-byte one costs two).
+// 16- or 32-byte one, i.e. half or all of the sector the memory system moves anyway (measured on
+// B200 over an L2-resident region: 16-byte random gathers run at three quarters of the rate of
+// 8-byte ones, 16-byte vector reductions at the same rate as 8-byte ones; a 32-byte access is two
+// 16-byte ones).
 //
 // What each kernel replaces in the reference (paths relative to its root):
 //   forward_kernel          kernels/permutohedral_encoding/EncodingGPU.cuh:68-256

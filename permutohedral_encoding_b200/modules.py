@@ -23,9 +23,9 @@ class PermutoEncoding(torch.nn.Module):
     unusable 1-element shift (modules.py:34 fails the native shape checks); here the shift is
     a zero ``[nr_levels, pos_dim]`` tensor, which is what the flag means.
     ``nr_feat_per_level`` may be 2 (the only width the reference implements), 4 or 8: a table
-    access moves a 32-byte sector whatever it uses of it, and a random access costs about the same
-    whether it moves 8 or 16 bytes, so e.g. 12 levels of 4 features produce 48 outputs in 60 % of
-    the time of 24 x 2.
+    access moves a 32-byte sector whatever it uses of it (16-byte random gathers run at three
+    quarters of the rate of 8-byte ones, 16-byte reductions at the same rate), so e.g. 12 levels
+    of 4 features produce 48 outputs in 60 % of the time of 24 x 2.
     ``concat_points_grad=True`` completes the position gradient of ``concat_points``: the
     reference (and the default here) gives the positions no gradient through the concatenated raw
     coordinates, because its backward skips those columns (src/Encoding.cu:129-134).
