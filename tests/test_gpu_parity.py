@@ -689,3 +689,65 @@ def test_concat_points_position_gradient_on_request(nat, oracle):
     x = pos.clone().requires_grad_(True)
     m(x, anneal).backward(go)
     assert torch.allclose(x.grad, pg_full, rtol=1e-4, atol=1e-4 * float(pg_full.abs().max()))
+
+
+def test_module_refuses_other_dtypes_and_reads_the_reference_no_shift_checkpoint(nat):
+    """.half()/.double() are refused where they are asked for (the kernels compute in fp32 only)
+    and leave the module usable; a reference checkpoint saved with
+    appply_random_shift_per_level=False (a 1-element, uninitialised shift) loads as the zero shift."""
+    from permutohedral_encoding_b200 import PermutoEncoding
+    sig = np.geomspace(1.0, 1e-2, 6)
+    torch.manual_seed(9)
+    m = PermutoEncoding(3, 2 ** 10, 6, 2, sig, appply_random_shift_per_level=False)
+    assert torch.count_nonzero(m.random_shift_per_level) == 0
+    pts = torch.rand(100, 3, device=DEV)
+    with torch.no_grad():
+        before = m(pts)
+    for convert in (m.half, m.double):
+        with pytest.raises(RuntimeError, match="float32 only"):
+            convert()
+    assert m.lattice_values.dtype == torch.float32 and m.anneal_window.dtype == torch.float32
+    with torch.no_grad():
+        assert torch.equal(m(pts), before)
+    state = {"lattice_values": m.lattice_values.detach().clone() * 2, "random_shift_per_level": torch.empty(1)}
+    m.load_state_dict(state)
+    assert m.random_shift_per_level.shape == (6, 3) and torch.count_nonzero(m.random_shift_per_level) == 0
+    with torch.no_grad():
+        assert torch.allclose(m(pts), 2 * before, rtol=1e-6, atol=0)
+    # a module WITH a shift still insists on the regular shape
+    m2 = PermutoEncoding(3, 2 ** 10, 6, 2, sig)
+    with pytest.raises(RuntimeError):
+        m2.load_state_dict(state)
+
+
+def test_remembered_static_inputs_follow_their_tensors(nat):
+    """The wrapper remembers the validated table / shift / window between calls; anything that
+    changes them -- other tensors, other memory, in-place updates, a window living on the CPU that
+    is edited in place -- must show in the next call's output."""
+    c, inp = cases.CASES["train_d3"], cases.make_inputs("train_d3")
+    enc, fx = make_encoding(nat, c, inp)
+    pos = T(inp["positions"])
+    table, anneal = T(inp["table"]), T(inp["anneal"])
+
+    def run(t, w):
+        return enc.forward(nat.EncodingInput(t, pos, w, False, False))
+
+    base = run(table, anneal)
+    tol = 1e-6 * float(base.abs().max())                               # scaling commutes up to fp32 rounding
+    assert torch.equal(run(table, anneal), base)                       # remembered
+    table2 = table * 3.0                                               # another tensor
+    assert torch.allclose(run(table2, anneal), 3.0 * base, rtol=1e-4, atol=tol)
+    table2.mul_(2.0)                                                   # same tensor, updated in place
+    assert torch.allclose(run(table2, anneal), 6.0 * base, rtol=1e-4, atol=tol)
+    half_window = anneal * 0.5
+    assert torch.allclose(run(table, half_window), 0.5 * base, rtol=1e-4, atol=tol)
+    cpu_window = torch.ones(c["nr_levels"])                            # converted copy: never remembered
+    assert torch.equal(run(table, cpu_window), base)
+    cpu_window.mul_(0.25)
+    assert torch.allclose(run(table, cpu_window), 0.25 * base, rtol=1e-4, atol=tol)
+    fx.m_random_shift_per_level = fx.m_random_shift_per_level + 1.0    # the module re-binds the shift like this
+    assert not torch.equal(run(table, anneal), base)
+    with pytest.raises(RuntimeError, match="anneal_window"):
+        run(table, torch.ones(c["nr_levels"] + 1, device=DEV))
+    with pytest.raises(RuntimeError, match="lattice_values should be"):
+        run(table[:, :-1].contiguous(), anneal)
