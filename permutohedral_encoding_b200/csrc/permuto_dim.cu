@@ -500,7 +500,7 @@ __global__ void __launch_bounds__(kTileRows, (F == 2 ? PERMUTO_FUSED_MIN_BLOCKS 
     // the last commit covers the whole product
     const int last = ksteps - 1;
     ok = umma::wait_bounded(umma::smem_u32(&slice_free[last % kRing]), (uint32_t)((last / kRing) & 1)) && ok;
-    ok = __syncthreads_and(ok) != 0;  // block-uniform verdict: tcgen05.ld below must be executed by whole warps
+    ok = __syncthreads_and(ok) != 0;  // block-uniform result: tcgen05.ld below must be executed by whole warps
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (!ok && a.status && t == 0) atomicExch(a.status, 1);
 
