@@ -23,6 +23,7 @@ same way in both arms (``--impl ours`` and ``--impl reference``):
                         (the reference's examples/performance.py loop)
   forward_linear        inference of the train workload followed by Linear(48, 32), the first layer
                         of the reference's toy MLP; this repo runs it as one fused kernel
+  forward_mlp           the same with the toy example's whole MLP (48-32-32-32-1, GELU) fused
 
 Rank 0 prints ONE JSON line.  ``value`` is whole-job Mpoints/s with inputs resident in HBM,
 timed on the device with CUDA events (max over ranks, median over repeats of K steps);
@@ -63,7 +64,7 @@ def parse_args():
     ap.add_argument("--clear", default="inline", choices=["inline", "early"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--blocks", default=None,
-                    help="comma-separated per-configuration blocks to add at N = 1 (train, forward_linear, "
+                    help="comma-separated per-configuration blocks to add at N = 1 (train, forward_linear, forward_mlp, "
                          "train_with_optimizer, readme_forward, eikonal, dim4, dim6); default: all of them for the "
                          "sharded workload, none otherwise")
     ap.add_argument("--no-blocks", action="store_true", help="same as --blocks ''")
@@ -528,6 +529,36 @@ def block_forward_linear(impl, runner, pos, device, steps):
     return blk
 
 
+def block_forward_mlp(impl, runner, pos, device, steps):
+    """Inference of the encoding followed by the WHOLE network of the reference's toy example
+    (examples/train_toy_example.py:18-26): Linear(48,32) GELU Linear(32,32) GELU Linear(32,32) GELU
+    Linear(32,1), on the train workload.  Ours: one fused kernel; beside it the unfused pair."""
+    gen = torch.Generator(device="cpu").manual_seed(78)
+    width = runner.encode(pos[:8]).shape[1]
+    mlp = torch.nn.Sequential(torch.nn.Linear(width, 32), torch.nn.GELU(), torch.nn.Linear(32, 32), torch.nn.GELU(),
+                              torch.nn.Linear(32, 32), torch.nn.GELU(), torch.nn.Linear(32, 1))
+    with torch.no_grad():
+        for m in mlp:
+            if isinstance(m, torch.nn.Linear):
+                m.weight.copy_(torch.randn(m.weight.shape, generator=gen) * (2.0 / m.in_features) ** 0.5)
+                m.bias.copy_(torch.randn(m.bias.shape, generator=gen) * 0.1)
+    mlp = mlp.to(device)
+    n = pos.shape[0]
+    with torch.no_grad():
+        ms_pair, reps = timed(lambda: mlp(runner.encode(pos)), steps, 3, device, 0.2, local_sync)
+        blk = {"unit": "Mpoints/s", "network": "48-32-32-32-1, GELU",
+               "what": "train workload, inference: encoding followed by the toy example's MLP"}
+        if impl == "ours":
+            ms_fused, reps = timed(lambda: runner.m.forward_mlp(pos, mlp), steps, 3, device, 0.2, local_sync)
+            blk.update({"value": round(n / ms_fused / 1e3, 2), "ms_per_step": round(ms_fused, 4), "repeats": reps,
+                        "unfused": {"value": round(n / ms_pair / 1e3, 2), "ms_per_step": round(ms_pair, 4),
+                                    "what": "module forward, then the torch.nn.Sequential"},
+                        "hbm_bytes_per_point": {"fused": 4 * 3 + 4, "unfused": 4 * 3 + 4 * width * 2 + 4 * 32 * 6 + 4 * 32 * 6 + 4}})
+        else:
+            blk.update({"value": round(n / ms_pair / 1e3, 2), "ms_per_step": round(ms_pair, 4), "repeats": reps})
+    return blk
+
+
 def allreduce_check(runner, pos, grad_out, device):
     """Outside the timed region: the gradient the overlapped, bucketed all-reduce left in .grad
     against a plain all-reduce of an un-hooked local backward.  Largest error relative to the
@@ -571,7 +602,8 @@ def main():
     if args.total_points:
         w["total_points"] = int(args.total_points)
     d, L = w["pos_dim"], w["nr_levels"]
-    all_blocks = ["train", "forward_linear", "train_with_optimizer", "readme_forward", "eikonal", "dim4", "dim6"]
+    all_blocks = ["train", "forward_linear", "forward_mlp", "train_with_optimizer", "readme_forward", "eikonal", "dim4",
+                  "dim6"]
     if args.no_blocks or WORLD > 1:
         blocks = []
     elif args.blocks is not None:
@@ -669,12 +701,14 @@ def main():
         del runner, pos, grad_out, feeder
         torch.cuda.empty_cache()
         ceil2 = ceilings if args.impl == "ours" else None
-        if {"train", "forward_linear", "train_with_optimizer"} & set(blocks):
+        if {"train", "forward_linear", "forward_mlp", "train_with_optimizer"} & set(blocks):
             blk, r2, p2 = block_train(args.impl, "train", device, args.steps, ceil2)
             if "train" in blocks:
                 line["train"] = blk
             if "forward_linear" in blocks:
                 line["forward_linear"] = block_forward_linear(args.impl, r2, p2, device, args.steps)
+            if "forward_mlp" in blocks:
+                line["forward_mlp"] = block_forward_mlp(args.impl, r2, p2, device, args.steps)
             if "train_with_optimizer" in blocks:
                 line["train_with_optimizer"] = block_optimizer(args.impl, r2, p2, device, args.steps)
             del r2, p2

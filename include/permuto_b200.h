@@ -132,6 +132,30 @@ int permuto_forward_linear(const permuto_config *cfg, const permuto_inputs *in, 
                            const float *bias, int32_t out_features, float *out, int32_t *status,
                            void *stream);
 
+/* One layer of the network behind the encoding: y = x @ weight^T + bias, weight row-major
+ * [out_features, in_features] (torch.nn.Linear layout), bias [out_features] or NULL; device pointers. */
+typedef struct permuto_mlp_layer {
+    const float *weight;
+    const float *bias;
+    int32_t in_features;
+    int32_t out_features;
+} permuto_mlp_layer;
+
+enum { PERMUTO_ACT_NONE = 0, PERMUTO_ACT_RELU = 1, PERMUTO_ACT_GELU = 2 /* exact, erf-based: torch.nn.GELU() */ };
+
+/* Forward fused with the WHOLE small network that consumes the features, e.g. the reference's
+ * toy example (examples/train_toy_example.py:18-26): Linear(48,32) GELU Linear(32,32) GELU
+ * Linear(32,32) GELU Linear(32,1).  One kernel: neither the features nor any hidden activation is
+ * written to memory; every layer with a width that is a multiple of 16 runs on the tensor cores
+ * (tf32 operands, fp32 accumulation in tensor memory), a narrower last layer (1..15 outputs) as
+ * fp32 dot products in registers.  `layers` is a HOST array of nr_layers (1..6) descriptors with
+ * layers[0].in_features == W and layers[i].in_features == layers[i-1].out_features; hidden widths
+ * are multiples of 16 in 16..64; the last layer has 1..16 outputs, or a multiple of 16 up to 64
+ * (up to 256 when it is the only layer).  `activation` is applied after every layer but the last.
+ * out is [N, out_features of the last layer]; status as for permuto_forward_linear.  Inference path. */
+int permuto_forward_mlp(const permuto_config *cfg, const permuto_inputs *in, const permuto_mlp_layer *layers,
+                        int32_t nr_layers, int32_t activation, float *out, int32_t *status, void *stream);
+
 /* First-order backward.  Replaces Encoding<P,2>::backward (src/Encoding.cu:111-215).
  * grad_features [N, W].  lattice_grad and positions_grad may each be NULL (not required).
  * Only levels in [level_begin, level_end) are processed -- pass 0 and nr_levels for all; a

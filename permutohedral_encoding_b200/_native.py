@@ -36,13 +36,14 @@ PERMUTO_ZERO_OUTPUTS = 1
 PERMUTO_NO_AGGREGATE = 2
 PERMUTO_KEEP_POSITIONS_GRAD = 4
 PERMUTO_CONCAT_POSITIONS_GRAD = 8
+PERMUTO_ACT = {"none": 0, "relu": 1, "gelu": 2}
 PERMUTO_ADAM_SKIP_UNTOUCHED = 1
 PERMUTO_ADAM_ZERO_GRAD = 2
 
 EXPORTED_SYMBOLS = (
     "permuto_abi_version", "permuto_last_error", "permuto_extra_levels", "permuto_scale_factor",
     "permuto_forward", "permuto_backward", "permuto_double_backward", "permuto_debug_lattice",
-    "permuto_probe_random_access", "permuto_adam_step", "permuto_forward_linear",
+    "permuto_probe_random_access", "permuto_adam_step", "permuto_forward_linear", "permuto_forward_mlp",
 )
 
 
@@ -50,6 +51,10 @@ class PermutoConfig(C.Structure):
     _fields_ = [("pos_dim", C.c_int32), ("nr_feat_per_level", C.c_int32), ("nr_levels", C.c_int32),
                 ("capacity", C.c_int32), ("concat_points", C.c_int32), ("points_scaling", C.c_float),
                 ("levels_per_pass", C.c_int32), ("table_dtype", C.c_int32)]
+
+
+class PermutoMlpLayer(C.Structure):
+    _fields_ = [("weight", C.c_void_p), ("bias", C.c_void_p), ("in_features", C.c_int32), ("out_features", C.c_int32)]
 
 
 class PermutoInputs(C.Structure):
@@ -87,6 +92,9 @@ def _load() -> C.CDLL:
                                                 C.c_void_p]
     lib.permuto_forward_linear.restype = C.c_int
     lib.permuto_forward_linear.argtypes = [cfgp, inp, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.permuto_forward_mlp.restype = C.c_int
+    lib.permuto_forward_mlp.argtypes = [cfgp, inp, C.POINTER(PermutoMlpLayer), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                        C.c_void_p]
     lib.permuto_adam_step.restype = C.c_int
     lib.permuto_adam_step.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_double, C.c_double,
                                       C.c_double, C.c_double, C.c_double, C.c_int64, C.c_uint32, C.c_void_p]
@@ -374,6 +382,49 @@ class EncodingWrapper:
             ins, keep = self._inputs(inp)
             check(lib.permuto_forward_linear(C.byref(cfg), C.byref(ins), _ptr(weight), _ptr(bias), h, _ptr(out),
                                              _ptr(status), _stream(dev)))
+        return out
+
+    def forward_mlp(self, inp: EncodingInput, layers, activation: str = "gelu", status=None) -> torch.Tensor:
+        """The encoding followed by a whole small MLP in one kernel: ``layers`` is a sequence of
+        ``(weight [out, in], bias [out] | None)`` pairs, ``activation`` ("none", "relu", "gelu")
+        is applied after every layer but the last.  Neither the features nor the hidden
+        activations reach memory; layers whose width is a multiple of 16 run on the tensor cores
+        (tf32 operands, fp32 accumulation), a narrower last layer as fp32 dot products.  Hidden
+        widths: multiples of 16 up to 64.  No gradients.  The reference's toy example network
+        (examples/train_toy_example.py:18-26) is the model case."""
+        pos = inp.m_positions_raw
+        dev = pos.device
+        if activation not in PERMUTO_ACT:
+            raise RuntimeError(f"activation must be one of {sorted(PERMUTO_ACT)}, got {activation!r}")
+        layers = list(layers)
+        if not 1 <= len(layers) <= 6:
+            raise RuntimeError(f"the fused network takes 1..6 layers, got {len(layers)}")
+        descr = (PermutoMlpLayer * len(layers))()
+        keep_alive = []
+        width = self.output_width()
+        for i, (weight, bias) in enumerate(layers):
+            if weight.dim() != 2 or weight.shape[1] != width:
+                raise RuntimeError(f"layer {i}: weight should be out_features x {width}, got {tuple(weight.shape)}")
+            weight = weight.detach()
+            if weight.device != dev or weight.dtype != torch.float32 or not weight.is_contiguous():
+                weight = weight.to(device=dev, dtype=torch.float32).contiguous()
+            if bias is not None:
+                bias = bias.detach()
+                if tuple(bias.shape) != (weight.shape[0],):
+                    raise RuntimeError(f"layer {i}: bias should have {weight.shape[0]} entries")
+                if bias.device != dev or bias.dtype != torch.float32 or not bias.is_contiguous():
+                    bias = bias.to(device=dev, dtype=torch.float32).contiguous()
+            keep_alive += [weight, bias]
+            descr[i] = PermutoMlpLayer(weight.data_ptr(), _ptr(bias), int(weight.shape[1]), int(weight.shape[0]))
+            width = int(weight.shape[0])
+        if status is not None and (status.dtype != torch.int32 or status.device != dev or status.numel() != 1):
+            raise RuntimeError("status should be a one-element int32 tensor on the device of the positions")
+        with _guard(dev):
+            ins, keep = self._inputs(inp)   # validates
+            cfg = self._config(inp)
+            out = torch.empty((pos.shape[0], width), dtype=torch.float32, device=dev)
+            check(lib.permuto_forward_mlp(C.byref(cfg), C.byref(ins), descr, len(layers), PERMUTO_ACT[activation],
+                                          out.data_ptr(), _ptr(status), _stream(dev)))
         return out
 
     def backward(self, inp: EncodingInput, grad_features: torch.Tensor, lattice_grad_out=None,

@@ -169,30 +169,77 @@ int permuto_forward(const permuto_config* cfg, const permuto_inputs* in, float* 
     return PERMUTO_OK;
 }
 
-int permuto_forward_linear(const permuto_config* cfg, const permuto_inputs* in, const float* weight, const float* bias,
-                           int32_t out_features, float* out, int32_t* status, void* stream) {
+int permuto_forward_mlp(const permuto_config* cfg, const permuto_inputs* in, const permuto_mlp_layer* layers,
+                        int32_t nr_layers, int32_t activation, float* out, int32_t* status, void* stream) {
     permuto::ForwardLinearArgs a;
     if (int rc = build_problem(cfg, in, a.p)) return rc;
-    if (!weight || !out) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "weight and out must not be NULL");
-    if (out_features < 16 || out_features > 256 || out_features % 16 != 0)
-        return set_error(PERMUTO_ERR_UNSUPPORTED, "out_features must be a multiple of 16 in 16..256 (got %d)", out_features);
+    if (!layers || !out) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "layers and out must not be NULL");
+    if (nr_layers < 1 || nr_layers > permuto::kMaxMlpLayers)
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "nr_layers must be in 1..%d (got %d)", permuto::kMaxMlpLayers, nr_layers);
+    if (activation != PERMUTO_ACT_NONE && activation != PERMUTO_ACT_RELU && activation != PERMUTO_ACT_GELU)
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "activation must be PERMUTO_ACT_NONE, _RELU or _GELU (got %d)", activation);
     if (a.p.width > 256)
-        return set_error(PERMUTO_ERR_UNSUPPORTED, "the fused layer takes feature rows of at most 256 columns (got %d)",
+        return set_error(PERMUTO_ERR_UNSUPPORTED, "the fused layers take feature rows of at most 256 columns (got %d)",
                          a.p.width);
-    if (!aligned(out, 16) || !aligned(weight, 4))
-        return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "out must be 16-byte aligned");
-    a.weight = weight;
-    a.bias = bias;
+    int widest = 0;  // over the layers that run on the tensor core
+    for (int i = 0; i < nr_layers; ++i) {
+        const permuto_mlp_layer& ly = layers[i];
+        const int expect = i == 0 ? a.p.width : layers[i - 1].out_features;
+        if (!ly.weight) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "layer %d: weight must not be NULL", i);
+        if (ly.in_features != expect)
+            return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "layer %d: in_features is %d but its input has %d columns", i,
+                             ly.in_features, expect);
+        const bool is_last = i == nr_layers - 1;
+        const int h = ly.out_features;
+        const bool on_tensor_core = h % 16 == 0 && h >= 16;
+        if (nr_layers == 1) {
+            if (!on_tensor_core || h > 256)
+                return set_error(PERMUTO_ERR_UNSUPPORTED, "out_features must be a multiple of 16 in 16..256 (got %d)", h);
+        } else if (!is_last) {
+            if (!on_tensor_core || h > 64)
+                return set_error(PERMUTO_ERR_UNSUPPORTED, "layer %d: a hidden width must be a multiple of 16 in 16..64 (got %d)", i, h);
+        } else if (!(on_tensor_core && h <= 64) && !(h >= 1 && h < 16)) {
+            return set_error(PERMUTO_ERR_UNSUPPORTED,
+                             "layer %d: the last layer must have 1..16 outputs or a multiple of 16 up to 64 (got %d)", i, h);
+        }
+        if (on_tensor_core && h > widest) widest = h;
+        a.layer[i].weight = ly.weight;
+        a.layer[i].bias = ly.bias;
+        a.layer[i].in_features = ly.in_features;
+        a.layer[i].out_features = h;
+    }
+    const int last_out = layers[nr_layers - 1].out_features;
+    if (!aligned(out, last_out % 16 == 0 ? 16 : 4)) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "out must be 16-byte aligned");
+    a.nr_layers = nr_layers;
+    a.activation = activation;
     a.out = out;
-    a.out_features = out_features;
     a.k_pad = (a.p.width + 7) / 8 * 8;
+    int half = 16;  // two accumulator ranges for the hidden layers to alternate between
+    while (half < widest) half <<= 1;
+    int cols = 32;  // allocation granularity of tensor memory: a power of two, at least 32 columns
+    while (cols < (nr_layers == 1 ? widest : 2 * half)) cols <<= 1;
+    a.tmem_cols = cols;
+    a.tmem_half = half;
     a.status = status;
-    a.out_vec8_ok = aligned(out, 32) ? 1 : 0;
+    a.out_vec8_ok = (last_out % 16 == 0 && aligned(out, 32)) ? 1 : 0;
     cudaError_t err;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     PERMUTO_DISPATCH(launch_forward_linear, a, st)
-    if (err != cudaSuccess) return cuda_fail(err, "permuto_forward_linear launch");
+    if (err != cudaSuccess) return cuda_fail(err, "permuto_forward_mlp launch");
     return PERMUTO_OK;
+}
+
+int permuto_forward_linear(const permuto_config* cfg, const permuto_inputs* in, const float* weight, const float* bias,
+                           int32_t out_features, float* out, int32_t* status, void* stream) {
+    if (!cfg || !in) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "cfg and in must not be NULL");
+    if (!weight || !out) return set_error(PERMUTO_ERR_INVALID_ARGUMENT, "weight and out must not be NULL");
+    permuto_mlp_layer one;
+    one.weight = weight;
+    one.bias = bias;
+    one.in_features = cfg->nr_feat_per_level * (cfg->nr_levels + extra_levels(cfg->pos_dim, cfg->nr_feat_per_level,
+                                                                              cfg->concat_points));
+    one.out_features = out_features;
+    return permuto_forward_mlp(cfg, in, &one, 1, PERMUTO_ACT_NONE, out, status, stream);
 }
 
 int permuto_backward(const permuto_config* cfg, const permuto_inputs* in, const float* grad_features,

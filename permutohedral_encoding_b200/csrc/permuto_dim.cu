@@ -381,33 +381,118 @@ constexpr int kTileRows = 128;  // points per block = rows of one tcgen05.mma
 #ifndef PERMUTO_FUSED_RING
 #define PERMUTO_FUSED_RING 2
 #endif
-constexpr int kRing = PERMUTO_FUSED_RING;  // 128 x 8 feature slices in flight between the encoder and the tensor core
+constexpr int kRing = PERMUTO_FUSED_RING;  // 128 x 8 slices in flight between the threads and the tensor core
 constexpr uint32_t kSliceBytes = kTileRows * 8 * 4;  // one slice: 128 rows x 8 tf32 = 4 KB
 
-// The feature tile is never whole in shared memory: every step of 8 columns is one K = 8 slice of
-// the product, written into a ring of kRing slices and consumed by one tcgen05.mma right away
-// (accumulating in tensor memory).  That keeps the block at 8 KB + the weight instead of
-// 128 x K x 4 bytes, so that shared memory neither limits the resident blocks nor eats the L1
-// capacity the coarse levels' gathers live on.
+// The A operand of every product is never whole in shared memory: 8 columns of the 128-row tile
+// (a K = 8 slice of the product) are written into a ring of kRing slices and consumed by one
+// tcgen05.mma right away, accumulating in tensor memory.  That keeps a block at 8 KB + the
+// weights instead of 128 x K x 4 bytes, so that shared memory neither limits the resident blocks
+// nor eats the L1 capacity the coarse levels' gathers live on.
+struct SliceRing {
+    unsigned char* base;   // kRing slices
+    uint64_t* free_bar;    // one mbarrier per slice: arrives when the MMA that read it is done
+    uint32_t base_addr;
+    uint32_t row_off;      // this thread's row inside a slice
+    int pushed;            // slices written so far (all layers)
+    bool ok;               // no bounded wait has run out
+
+    // Write this thread's 8 values of the next slice; when the whole block has, thread 0 issues
+    // D[128 x n] (+)= slice[128 x 8] * B[n x 8]^T and commits to the slice's barrier.
+    // Block-uniform control flow: every thread of the block calls it.
+    __device__ __forceinline__ void push(const float (&v)[8], uint32_t tmem_d, uint32_t b_addr, uint32_t b_stride,
+                                         uint32_t idesc, bool accumulate) {
+        const int slot = pushed % kRing;
+        // the MMA that read this slice kRing pushes ago must be done before it is overwritten
+        if (pushed >= kRing) ok = umma::wait_bounded(umma::smem_u32(&free_bar[slot]), (uint32_t)((pushed / kRing - 1) & 1)) && ok;
+        unsigned char* dst = base + (size_t)slot * kSliceBytes + row_off;
+        *reinterpret_cast<float4*>(dst) =
+            make_float4(umma::to_tf32(v[0]), umma::to_tf32(v[1]), umma::to_tf32(v[2]), umma::to_tf32(v[3]));
+        *reinterpret_cast<float4*>(dst + 128) =
+            make_float4(umma::to_tf32(v[4]), umma::to_tf32(v[5]), umma::to_tf32(v[6]), umma::to_tf32(v[7]));
+        // the block's writes -> visible to the tensor core (async proxy); then one thread issues the slice's MMA
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            umma::mma_tf32(tmem_d, umma::smem_desc(base_addr + (uint32_t)slot * kSliceBytes, 128u, 256u),
+                           umma::smem_desc(b_addr, 128u, b_stride), idesc, accumulate);
+            umma::commit(umma::smem_u32(&free_bar[slot]));  // covers every MMA issued so far
+        }
+        ++pushed;
+    }
+
+    // Wait until every MMA issued so far is done (the last commit covers them all); the result is
+    // made block-uniform, because tcgen05.ld afterwards must be executed by whole warps.
+    __device__ __forceinline__ bool drain() {
+        const int last = pushed - 1;
+        ok = umma::wait_bounded(umma::smem_u32(&free_bar[last % kRing]), (uint32_t)((last / kRing) & 1)) && ok;
+        ok = __syncthreads_and(ok) != 0;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        return ok;
+    }
+};
+
+// weight [rows, cols] row-major in global memory -> shared memory in the K-major operand layout
+// with `chunks` 16-byte column groups per row, rounded to tf32; columns beyond `cols` are zero
+__device__ __forceinline__ void stage_weight(unsigned char* tile, const float* __restrict__ weight, int rows, int cols,
+                                             int chunks) {
+    const uint32_t stride = (uint32_t)chunks * 128u;
+    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(weight) & 15u) == 0);
+    for (int e = threadIdx.x; e < rows * chunks; e += kTileRows) {
+        const int n = e / chunks, kc = e - n * chunks;
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* src = weight + (size_t)n * cols + 4 * kc;
+        if (vec && 4 * kc + 3 < cols) {
+            w = __ldg(reinterpret_cast<const float4*>(src));
+        } else {
+            if (4 * kc + 0 < cols) w.x = __ldg(src + 0);
+            if (4 * kc + 1 < cols) w.y = __ldg(src + 1);
+            if (4 * kc + 2 < cols) w.z = __ldg(src + 2);
+            if (4 * kc + 3 < cols) w.w = __ldg(src + 3);
+        }
+        *reinterpret_cast<float4*>(tile + (size_t)(n >> 3) * stride + (size_t)kc * 128 + (n & 7) * 16) =
+            make_float4(umma::to_tf32(w.x), umma::to_tf32(w.y), umma::to_tf32(w.z), umma::to_tf32(w.w));
+    }
+}
+
+// 16 consecutive accumulator columns of this thread's row (tensor-memory lane = row)
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));  // all 32 lanes of the warp take part
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float activate(float x, int kind) {
+    if (kind == PERMUTO_ACT_RELU) return fmaxf(x, 0.f);
+    if (kind == PERMUTO_ACT_GELU) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));  // torch.nn.GELU()
+    return x;
+}
+
 #ifndef PERMUTO_FUSED_MIN_BLOCKS
 #define PERMUTO_FUSED_MIN_BLOCKS 8
 #endif
-template <int F, int LPS, bool HALF>
-__global__ void __launch_bounds__(kTileRows, (F == 2 ? PERMUTO_FUSED_MIN_BLOCKS : 4)) forward_linear_kernel(const ForwardLinearArgs a) {
+// HMAX = 0: the encoding followed by ONE linear layer (out = features @ W^T + b).
+// HMAX = 32 / 64: a whole small MLP behind the encoding; hidden widths are multiples of 16 up to
+// HMAX (a thread holds its row of hidden activations in registers between two layers).
+template <int F, int LPS, bool HALF, int HMAX>
+__global__ void __launch_bounds__(kTileRows, (F == 2 && HMAX <= 32 ? PERMUTO_FUSED_MIN_BLOCKS : 4))
+forward_mlp_kernel(const ForwardLinearArgs a) {
     const Problem& p = a.p;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int chunks = a.k_pad / 4;                         // 16-byte column groups per weight row
-    const uint32_t b_stride = (uint32_t)chunks * 128u;      // weight: between 8-row groups
-    unsigned char* ring = smem_raw;                         // kRing slices of [128 x 8]
-    unsigned char* tile_b = smem_raw + kRing * kSliceBytes; // [H x k_pad] weight
-    __shared__ __align__(8) uint64_t slice_free[kRing];     // arrives when the MMA that read the slice is done
+    __shared__ __align__(8) uint64_t slice_free[kRing];
     __shared__ uint32_t tmem_base;
 
     const int t = threadIdx.x;
     const int warp = t >> 5;
-    const int H = a.out_features;
-    uint32_t tmem_cols = 32;  // allocation granularity: a power of two, at least 32 columns
-    while ((int)tmem_cols < H) tmem_cols <<= 1;
+    const int H0 = a.layer[0].out_features;
+    const uint32_t tmem_cols = (uint32_t)a.tmem_cols;  // a power of two >= 32 (host-computed)
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(umma::smem_u32(&tmem_base)),
@@ -422,116 +507,156 @@ __global__ void __launch_bounds__(kTileRows, (F == 2 ? PERMUTO_FUSED_MIN_BLOCKS 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 
-    // weight -> shared memory in the operand layout, rounded to tf32; columns beyond the row width are zero
-    const bool w_vec = (p.width % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.weight) & 15u) == 0);
-    for (int e = t; e < H * chunks; e += kTileRows) {
-        const int n = e / chunks, kc = e - n * chunks;
-        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float* src = a.weight + (size_t)n * p.width + 4 * kc;
-        if (w_vec && 4 * kc + 3 < p.width) {
-            w = __ldg(reinterpret_cast<const float4*>(src));
-        } else {
-            if (4 * kc + 0 < p.width) w.x = __ldg(src + 0);
-            if (4 * kc + 1 < p.width) w.y = __ldg(src + 1);
-            if (4 * kc + 2 < p.width) w.z = __ldg(src + 2);
-            if (4 * kc + 3 < p.width) w.w = __ldg(src + 3);
+    // shared memory: the slice ring, then the weight of every layer that runs on the tensor core
+    unsigned char* tile_w = smem_raw + kRing * kSliceBytes;
+    const int chunks0 = a.k_pad / 4;
+    stage_weight(tile_w, a.layer[0].weight, H0, p.width, chunks0);
+    if (HMAX > 0) {
+        unsigned char* next = tile_w + (size_t)H0 * a.k_pad * 4;
+        for (int i = 1; i < a.nr_layers; ++i) {
+            const MlpLayer& ly = a.layer[i];
+            if (ly.out_features % 16 != 0) break;  // a narrow last layer is evaluated in registers
+            stage_weight(next, ly.weight, ly.out_features, ly.in_features, ly.in_features / 4);
+            next += (size_t)ly.out_features * ly.in_features * 4;
         }
-        *reinterpret_cast<float4*>(tile_b + (size_t)(n >> 3) * b_stride + (size_t)kc * 128 + (n & 7) * 16) =
-            make_float4(umma::to_tf32(w.x), umma::to_tf32(w.y), umma::to_tf32(w.z), umma::to_tf32(w.w));
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base;
-    const uint32_t idesc = umma::instr_desc_tf32(kTileRows, H);
-    const uint32_t addr_ring = umma::smem_u32(ring), addr_b = umma::smem_u32(tile_b);
 
-    // this thread's point -> row t of every slice
+    SliceRing ring;
+    ring.base = smem_raw;
+    ring.free_bar = slice_free;
+    ring.base_addr = umma::smem_u32(smem_raw);
+    ring.row_off = (uint32_t)(t >> 3) * 256u + (uint32_t)(t & 7) * 16u;  // 8-row groups 256 bytes apart
+    ring.pushed = 0;
+    ring.ok = true;
+
+    // ---- layer 0: this thread's point -> row t of every slice ----------------------------------
     const int64_t n_raw = (int64_t)blockIdx.x * kTileRows + t;
     const bool active = n_raw < p.n_points;
     const int64_t n = active ? n_raw : p.n_points - 1;  // idle rows shadow the last point and are not stored
-    float pos[D];
-    load_pos(p, n, pos);
-    const uint32_t row_off = (uint32_t)(t >> 3) * 256u + (uint32_t)(t & 7) * 16u;  // 8-row groups 256 bytes apart
-    const int lattice_cols = F * p.nr_levels;
-    // a column past the lattice levels: a concatenated raw coordinate (EncodingGPU.cuh:105-121) or padding
-    auto tail_value = [&](int c) -> float {
-        float v = 0.f;
-        const int i = c - lattice_cols;
+    {
+        float pos[D];
+        load_pos(p, n, pos);
+        const int lattice_cols = F * p.nr_levels;
+        // a column past the lattice levels: a concatenated raw coordinate (EncodingGPU.cuh:105-121) or padding
+        auto tail_value = [&](int c) -> float {
+            float v = 0.f;
+            const int i = c - lattice_cols;
 #pragma unroll
-        for (int j = 0; j < D; ++j) v = (i == j && c < p.width) ? pos[j] * p.points_scaling : v;
-        return v;
-    };
-    const int nsteps = (p.nr_levels + LPS - 1) / LPS;  // steps that hold lattice levels
-    const int ksteps = a.k_pad / 8;                    // all steps: one tcgen05.mma each
-    bool ok = true;
+            for (int j = 0; j < D; ++j) v = (i == j && c < p.width) ? pos[j] * p.points_scaling : v;
+            return v;
+        };
+        const int nsteps = (p.nr_levels + LPS - 1) / LPS;  // steps that hold lattice levels
+        const int ksteps = a.k_pad / 8;                    // all steps: one tcgen05.mma each
+        const uint32_t idesc = umma::instr_desc_tf32(kTileRows, H0);
+        const uint32_t addr_w = umma::smem_u32(tile_w);
 #pragma unroll 1
-    for (int s = 0; s < ksteps; ++s) {
-        float out[8];
+        for (int s = 0; s < ksteps; ++s) {
+            float out[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) out[i] = 0.f;
-        if (s < nsteps) encode_step<F, LPS, HALF>(p, pos, s * LPS, p.nr_levels, out);
-        if (8 * s + 8 > lattice_cols) {  // block-uniform: only the last step(s) reach past the lattice levels
+            for (int i = 0; i < 8; ++i) out[i] = 0.f;
+            if (s < nsteps) encode_step<F, LPS, HALF>(p, pos, s * LPS, p.nr_levels, out);
+            if (8 * s + 8 > lattice_cols) {  // block-uniform: only the last step(s) reach past the lattice levels
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int c = 8 * s + i;
-                out[i] = (c >= lattice_cols) ? tail_value(c) : out[i];
+                for (int i = 0; i < 8; ++i) {
+                    const int c = 8 * s + i;
+                    out[i] = (c >= lattice_cols) ? tail_value(c) : out[i];
+                }
             }
-        }
-        const int slot = s % kRing;
-        // the MMA that read this slice kRing steps ago must be done before it is overwritten
-        if (s >= kRing) ok = umma::wait_bounded(umma::smem_u32(&slice_free[slot]), (uint32_t)((s / kRing - 1) & 1)) && ok;
-        unsigned char* dst = ring + (size_t)slot * kSliceBytes + row_off;
-        *reinterpret_cast<float4*>(dst) =
-            make_float4(umma::to_tf32(out[0]), umma::to_tf32(out[1]), umma::to_tf32(out[2]), umma::to_tf32(out[3]));
-        *reinterpret_cast<float4*>(dst + 128) =
-            make_float4(umma::to_tf32(out[4]), umma::to_tf32(out[5]), umma::to_tf32(out[6]), umma::to_tf32(out[7]));
-        // the block's writes -> visible to the tensor core (async proxy); then one thread issues the slice's MMA
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (t == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            umma::mma_tf32(tmem, umma::smem_desc(addr_ring + (uint32_t)slot * kSliceBytes, 128u, 256u),
-                           umma::smem_desc(addr_b + (uint32_t)s * 256u, 128u, b_stride), idesc, s > 0);
-            umma::commit(umma::smem_u32(&slice_free[slot]));  // covers every MMA issued so far
+            ring.push(out, tmem, addr_w + (uint32_t)s * 256u, (uint32_t)chunks0 * 128u, idesc, s > 0);
         }
     }
-    // the last commit covers the whole product
-    const int last = ksteps - 1;
-    ok = umma::wait_bounded(umma::smem_u32(&slice_free[last % kRing]), (uint32_t)((last / kRing) & 1)) && ok;
-    ok = __syncthreads_and(ok) != 0;  // block-uniform result: tcgen05.ld below must be executed by whole warps
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (!ok && a.status && t == 0) atomicExch(a.status, 1);
 
-    // accumulator row t: tensor-memory lane 32*warp + lane, H consecutive columns, 16 at a time
-    if (ok) {
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        float* dst = a.out + n_raw * H;
-        for (int c = 0; c < H; c += 16) {
-            uint32_t r[16];
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(lane_base + (uint32_t)c));  // all 32 lanes of the warp take part
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (active) {
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);  // tensor-memory lane = 32*warp + lane = row t
+    bool ok = true;
+    int last = 0;          // layer whose accumulators are in tensor memory
+    uint32_t col = 0;      // ... starting at this column
+
+    // ---- hidden layers: accumulators -> registers (+bias, activation) -> slices -> next product ----
+    if (HMAX > 0) {
+        constexpr int HM = HMAX > 0 ? HMAX : 16;
+        uint32_t w_addr = umma::smem_u32(tile_w) + (uint32_t)H0 * (uint32_t)a.k_pad * 4u;
+        for (int i = 1; i < a.nr_layers; ++i) {
+            const MlpLayer& ly = a.layer[i];
+            const int width = ly.in_features;  // = out_features of layer i-1, a multiple of 16 up to HMAX
+            ok = ring.drain() && ok;
+            float h[HM];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+            for (int c = 0; c < HM / 16; ++c) {
+                if (16 * c < width) {
+                    float v[16];
+                    tmem_load16(lane_base + col + 16u * c, v);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        const float b = a.layer[i - 1].bias ? __ldg(a.layer[i - 1].bias + 16 * c + k) : 0.f;
+                        h[16 * c + k] = activate(v[k] + b, a.activation);
+                    }
+                }
+            }
+            if (ly.out_features % 16 != 0) {
+                // narrow last layer (e.g. one output): plain fp32 dot products in registers
+                if (active && ok) {
+                    for (int o = 0; o < ly.out_features; ++o) {
+                        float acc = ly.bias ? __ldg(ly.bias + o) : 0.f;
+                        const float* w = ly.weight + (size_t)o * width;
+#pragma unroll
+                        for (int k = 0; k < HM; ++k)
+                            if (k < width) acc = fmaf(h[k], __ldg(w + k), acc);
+                        a.out[n_raw * ly.out_features + o] = acc;
+                    }
+                }
+                last = -1;  // everything is written
+                break;
+            }
+            const uint32_t dst_col = col ^ (uint32_t)a.tmem_half;  // ping-pong between the two halves
+            const uint32_t idesc = umma::instr_desc_tf32(kTileRows, ly.out_features);
+#pragma unroll
+            for (int j = 0; j < HM / 8; ++j) {
+                if (8 * j < width) {
                     float v[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * h + i]) + (a.bias ? __ldg(a.bias + c + 8 * h + i) : 0.f);
-                    if (a.out_vec8_ok) {
-                        store8(dst + c + 8 * h, v);
-                    } else {
-                        reinterpret_cast<float4*>(dst + c + 8 * h)[0] = make_float4(v[0], v[1], v[2], v[3]);
-                        reinterpret_cast<float4*>(dst + c + 8 * h)[1] = make_float4(v[4], v[5], v[6], v[7]);
+                    for (int k = 0; k < 8; ++k) v[k] = h[8 * j + k];
+                    ring.push(v, tmem + dst_col, w_addr + (uint32_t)j * 256u, (uint32_t)(width / 4) * 128u, idesc, j > 0);
+                }
+            }
+            w_addr += (uint32_t)ly.out_features * (uint32_t)width * 4u;
+            col = dst_col;
+            last = i;
+        }
+    }
+
+    // ---- last tensor-core layer: accumulators + bias -> out[N, out_features] -------------------------
+    if (last >= 0) {
+        ok = ring.drain() && ok;
+        const int H = a.layer[last].out_features;
+        const float* bias = a.layer[last].bias;
+        if (ok) {
+            float* dst = a.out + n_raw * H;
+            for (int c = 0; c < H; c += 16) {
+                float v[16];
+                tmem_load16(lane_base + col + (uint32_t)c, v);
+                if (active) {
+#pragma unroll
+                    for (int h8 = 0; h8 < 2; ++h8) {
+                        float o[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) o[k] = v[8 * h8 + k] + (bias ? __ldg(bias + c + 8 * h8 + k) : 0.f);
+                        if (a.out_vec8_ok) {
+                            store8(dst + c + 8 * h8, o);
+                        } else {
+                            reinterpret_cast<float4*>(dst + c + 8 * h8)[0] = make_float4(o[0], o[1], o[2], o[3]);
+                            reinterpret_cast<float4*>(dst + c + 8 * h8)[1] = make_float4(o[4], o[5], o[6], o[7]);
+                        }
                     }
                 }
             }
         }
     }
+    if (!ok && a.status && t == 0) atomicExch(a.status, 1);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0)
@@ -975,7 +1100,12 @@ cudaError_t launch_forward(const ForwardArgs& a, cudaStream_t st) {
 
 template <int F, int LPS>
 cudaError_t launch_forward_linear(const ForwardLinearArgs& a, cudaStream_t st) {
-    const size_t smem = (size_t)kRing * kSliceBytes + (size_t)a.out_features * a.k_pad * sizeof(float);
+    size_t smem = (size_t)kRing * kSliceBytes + (size_t)a.layer[0].out_features * a.k_pad * sizeof(float);
+    int hmax = 0;  // widest hidden layer
+    for (int i = 1; i < a.nr_layers; ++i) {
+        if (a.layer[i].in_features > hmax) hmax = a.layer[i].in_features;
+        if (a.layer[i].out_features % 16 == 0) smem += (size_t)a.layer[i].out_features * a.layer[i].in_features * sizeof(float);
+    }
     const dim3 g((unsigned)((a.p.n_points + kTileRows - 1) / kTileRows));
     auto launch = [&](auto kernel) -> cudaError_t {
         if (smem + 1024 > 48 * 1024) {  // the kernel's few static shared words count against the default limit
@@ -985,7 +1115,10 @@ cudaError_t launch_forward_linear(const ForwardLinearArgs& a, cudaStream_t st) {
         kernel<<<g, kTileRows, smem, st>>>(a);
         return cudaGetLastError();
     };
-    return a.p.table_half ? launch(forward_linear_kernel<F, LPS, true>) : launch(forward_linear_kernel<F, LPS, false>);
+    const bool h = a.p.table_half != 0;
+    if (a.nr_layers == 1) return h ? launch(forward_mlp_kernel<F, LPS, true, 0>) : launch(forward_mlp_kernel<F, LPS, false, 0>);
+    if (hmax <= 32) return h ? launch(forward_mlp_kernel<F, LPS, true, 32>) : launch(forward_mlp_kernel<F, LPS, false, 32>);
+    return h ? launch(forward_mlp_kernel<F, LPS, true, 64>) : launch(forward_mlp_kernel<F, LPS, false, 64>);
 }
 
 // The table is only read where something is gathered (position gradient, grad-grad features):

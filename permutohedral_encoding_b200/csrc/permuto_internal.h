@@ -4,6 +4,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#include "permuto_b200.h"
+
 namespace permuto {
 
 // Everything a kernel needs to walk the lattice for a range of levels.
@@ -36,16 +38,26 @@ struct ForwardArgs {
     float* features;
 };
 
-// forward fused with the first linear layer of the consumer: out = features @ weight^T + bias
+// forward fused with the network that consumes the features: one linear layer
+// (out = features @ weight^T + bias) or a whole small MLP
+constexpr int kMaxMlpLayers = 6;
+struct MlpLayer {
+    const float* weight;   // [out_features, in_features] row-major (the layout of torch.nn.Linear.weight)
+    const float* bias;     // [out_features] or null
+    int32_t in_features;
+    int32_t out_features;
+};
 struct ForwardLinearArgs {
     Problem p;
-    const float* weight;   // [out_features, p.width] row-major (the layout of torch.nn.Linear.weight)
-    const float* bias;     // [out_features] or null
-    float* out;            // [N, out_features]
-    int32_t out_features;  // multiple of 16, 16..256
+    MlpLayer layer[kMaxMlpLayers];  // layer[0].in_features == p.width
+    int32_t nr_layers;
+    int32_t activation;    // PERMUTO_ACT_*, applied after every layer but the last
+    float* out;            // [N, out_features of the last layer]
     int32_t k_pad;         // p.width rounded up to a multiple of 8 (one tf32 MMA consumes 8)
+    int32_t tmem_cols;     // tensor-memory columns per block: a power of two >= 32
+    int32_t tmem_half;     // column offset of the second accumulator range (hidden layers ping-pong)
     int32_t* status;       // device word set non-zero when a wait on the tensor core ran out
-    int32_t out_vec8_ok;   // out is 32-byte aligned (rows are multiples of 64 bytes): 256-bit stores
+    int32_t out_vec8_ok;   // out rows can be written with 256-bit stores
 };
 
 struct BackwardArgs {

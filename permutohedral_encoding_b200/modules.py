@@ -159,6 +159,45 @@ class PermutoEncoding(torch.nn.Module):
         inp = _C.EncodingInput(self.lattice_values, positions, anneal_window, False, False, half)
         return self.lattice.forward_linear(inp, weight, bias, status)
 
+    @torch.no_grad()
+    def forward_mlp(self, positions, mlp, anneal_window=None, status=None):
+        """Inference shortcut for ``mlp(self(positions))`` where ``mlp`` is a ``torch.nn.Sequential``
+        of ``Linear`` layers separated by one kind of activation (``GELU()`` or ``ReLU()``; none
+        after the last layer) -- e.g. the network of the reference's toy example
+        (examples/train_toy_example.py:18-26).  One kernel: neither the features nor the hidden
+        activations are written to memory; see ``EncodingWrapper.forward_mlp`` for the limits
+        (hidden widths multiples of 16 up to 64) and the precision (tf32 operands)."""
+        if anneal_window is None:
+            anneal_window = self.anneal_window
+        if anneal_window.device != positions.device:
+            anneal_window = anneal_window.to(positions.device)
+        self.fixed_params.m_random_shift_per_level = self.random_shift_per_level
+        layers, kinds = [], set()
+        mods = list(mlp)
+        prev = None
+        for m in mods:
+            if isinstance(m, torch.nn.Linear):
+                if isinstance(prev, torch.nn.Linear):
+                    kinds.add("none")     # two layers back to back
+                layers.append((m.weight, m.bias))
+            elif isinstance(m, (torch.nn.GELU, torch.nn.ReLU)):
+                if not isinstance(prev, torch.nn.Linear):
+                    raise RuntimeError("an activation must follow a Linear layer")
+                if isinstance(m, torch.nn.GELU) and getattr(m, "approximate", "none") != "none":
+                    raise RuntimeError("only the exact GELU (approximate='none') is fused")
+                kinds.add("gelu" if isinstance(m, torch.nn.GELU) else "relu")
+            else:
+                raise RuntimeError(f"cannot fuse a {type(m).__name__} layer")
+            prev = m
+        if not layers or not isinstance(mods[-1], torch.nn.Linear):
+            raise RuntimeError("the fused network must end with a Linear layer")
+        if len(kinds) > 1:
+            raise RuntimeError(f"one kind of activation between the layers, got {sorted(kinds)}")
+        activation = kinds.pop() if kinds else "none"
+        half = self._half_copy() if getattr(self, "half_precision_table", False) else None
+        inp = _C.EncodingInput(self.lattice_values, positions, anneal_window, False, False, half)
+        return self.lattice.forward_mlp(inp, layers, activation, status)
+
     def output_dims(self):
         nr_resolutions_extra = 0
         if self.concat_points:

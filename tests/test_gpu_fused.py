@@ -141,3 +141,120 @@ def test_forward_linear_rejects_bad_arguments(nat):
         == nat.PERMUTO_ERR_INVALID_ARGUMENT
     assert nat.lib.permuto_forward_linear(C.byref(cfg), C.byref(ins), 256, None, 40, 256, None, None) \
         == nat.PERMUTO_ERR_UNSUPPORTED
+
+
+# ---------------------------------------------------------------------------------------------
+# a whole small MLP behind the encoding
+# ---------------------------------------------------------------------------------------------
+def _tf32(x):
+    """cvt.rna.tf32.f32 in numpy: fp32 rounded to a 10-bit mantissa, ties away from zero."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((bits + np.uint32(0x1000)) & np.uint32(0xFFFFE000)).view(np.float32)
+
+
+def _mlp_reference(feats, layers, activation):
+    """Two float64 evaluations of the layers: exact, and with the operands of every tensor-core
+    layer (width a multiple of 16) rounded to tf32 as the kernel rounds them.  Also returns, per
+    output, sum|x*w| of the last layer (the magnitude the tolerances are relative to) and a
+    worst-case bound on exact-vs-tf32: every tensor-core layer perturbs its output by at most
+    TF32_RTOL * sum|x*w|, and a perturbation of a layer's input passes through |W| and an
+    activation whose slope is at most 1.13."""
+    from scipy.special import erf
+
+    def act(y):
+        if activation == "relu":
+            return np.maximum(y, 0)
+        if activation == "gelu":
+            return 0.5 * y * (1 + erf(y / np.sqrt(2.0)))
+        return y
+
+    x = xe = feats.astype(np.float64)
+    err = np.zeros_like(x)
+    for i, (w, b) in enumerate(layers):
+        w64 = w.astype(np.float64)
+        bias = 0 if b is None else b.astype(np.float64)
+        on_tensor_core = w.shape[0] % 16 == 0
+        err = err @ np.abs(w64).T + (TF32_RTOL * (np.abs(x) @ np.abs(w64).T) if on_tensor_core else 0)
+        mag = np.abs(xe) @ np.abs(w64).T
+        if on_tensor_core:
+            xe = _tf32(xe.astype(np.float32)).astype(np.float64) @ _tf32(w).astype(np.float64).T + bias
+        else:
+            xe = xe.astype(np.float32).astype(np.float64) @ w64.T + bias
+        x = x @ w64.T + bias
+        if i + 1 < len(layers):
+            x, xe, err = act(x), act(xe), err * 1.13
+    return x, err, xe, mag
+
+
+MLP_CASES = {
+    # the reference's toy example: 48 -> 32 -> 32 -> 32 -> 1 with GELU (examples/train_toy_example.py:18-26)
+    "toy_example": ("toy_mlp", [32, 32, 32, 1], "gelu", True),
+    "relu_two_outputs": ("toy_mlp", [64, 16, 3], "relu", True),
+    "wide_last": ("wide_64", [48, 32], "gelu", False),
+    "linear_chain": ("padded_concat", [16, 16], "none", True),
+    "feat4_hidden64": ("feat4", [64, 64, 4], "gelu", True),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MLP_CASES))
+def test_forward_mlp_against_oracle(nat, oracle, name):
+    base, widths, activation, with_bias = MLP_CASES[name]
+    c, inp, enc, fx, _, _ = _setup(nat, base)
+    import zlib
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    layers, fan_in = [], enc.output_width()
+    for h in widths:
+        w = (rng.standard_normal((h, fan_in)) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+        b = (rng.standard_normal(h) * 0.2).astype(np.float32) if with_bias else None
+        layers.append((w, b))
+        fan_in = h
+    scale = fx.m_scale_factor_host.numpy()
+    feats = oracle.forward(inp["positions"], inp["table"], scale, inp["shift"], inp["anneal"],
+                           concat_points=c.get("concat", False), points_scaling=c.get("points_scaling", 1.0))
+    want, err, emulated, mag = _mlp_reference(feats, layers, activation)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    I = nat.EncodingInput(T(inp["table"]), T(inp["positions"]), T(inp["anneal"]), False, False)
+    dev_layers = [(T(w), None if b is None else T(b)) for w, b in layers]
+    got = enc.forward_mlp(I, dev_layers, activation, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert got.shape == (c["n"], widths[-1])
+    got64 = got.cpu().numpy().astype(np.float64)
+    # sharp: the same roundings emulated in float64 -- what is left is fp32 accumulation and the odd
+    # hidden unit that lands on the other side of a tf32 rounding boundary
+    sharp = 1e-3 * mag + 1e-6 * np.abs(want).max()
+    assert np.all(np.abs(got64 - emulated) <= sharp), f"worst error / tolerance = {(np.abs(got64 - emulated) / sharp).max():.3f}"
+    assert np.abs(want).max() > 50 * sharp.mean()            # ... and that tolerance is not vacuous
+    # loose: the exact network, within the worst-case cost of tf32 operands
+    bound = err + 1e-5 * np.abs(want).max()
+    assert np.all(np.abs(got64 - want) <= bound)
+    # against the unfused evaluation in fp32 on the device
+    x = enc.forward(I)
+    for i, (w, b) in enumerate(dev_layers):
+        x = torch.nn.functional.linear(x, w, b)
+        if i + 1 < len(dev_layers):
+            x = {"gelu": torch.nn.functional.gelu, "relu": torch.relu, "none": lambda v: v}[activation](x)
+    assert np.all(np.abs((got - x).cpu().numpy()) <= bound + 1e-5 * np.abs(want).max())
+    assert torch.equal(got, enc.forward_mlp(I, dev_layers, activation))
+
+
+def test_forward_mlp_module_with_the_toy_example_network(nat):
+    from permutohedral_encoding_b200 import PermutoEncoding
+    torch.manual_seed(5)
+    enc = PermutoEncoding(3, 2 ** 16, 24, 2, np.geomspace(1.0, 1e-4, 24))
+    with torch.no_grad():
+        enc.lattice_values.uniform_(-1, 1)
+    mlp = torch.nn.Sequential(torch.nn.Linear(enc.output_dims(), 32), torch.nn.GELU(), torch.nn.Linear(32, 32),
+                              torch.nn.GELU(), torch.nn.Linear(32, 32), torch.nn.GELU(), torch.nn.Linear(32, 1)).to(DEV)
+    pts = torch.rand(70001, 3, device=DEV)
+    with torch.no_grad():
+        want = mlp(enc(pts))
+    got = enc.forward_mlp(pts, mlp)
+    assert got.shape == (70001, 1) and not got.requires_grad
+    assert torch.allclose(got, want, rtol=0, atol=5e-3 * float(want.abs().max()))
+    with pytest.raises(RuntimeError, match="end with a Linear"):
+        enc.forward_mlp(pts, torch.nn.Sequential(torch.nn.Linear(48, 32), torch.nn.GELU()).to(DEV))
+    with pytest.raises(RuntimeError, match="cannot fuse"):
+        enc.forward_mlp(pts, torch.nn.Sequential(torch.nn.Linear(48, 32), torch.nn.Tanh(), torch.nn.Linear(32, 1)).to(DEV))
+    with pytest.raises(RuntimeError, match="hidden width"):
+        enc.forward_mlp(pts, torch.nn.Sequential(torch.nn.Linear(48, 24), torch.nn.ReLU(), torch.nn.Linear(24, 1)).to(DEV))
