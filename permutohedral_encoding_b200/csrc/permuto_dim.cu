@@ -469,9 +469,19 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// erf to 1.5e-7 absolute (Abramowitz & Stegun 7.1.26) in about 15 instructions: the hidden
+// activations are rounded to tf32 (5e-4 relative) right afterwards, and erff() itself would be
+// most of the instructions of a hidden layer
+__device__ __forceinline__ float erf_fast(float x) {
+    const float ax = fabsf(x);
+    const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
+    const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
+    return copysignf(1.0f - poly * __expf(-ax * ax), x);
+}
+
 __device__ __forceinline__ float activate(float x, int kind) {
     if (kind == PERMUTO_ACT_RELU) return fmaxf(x, 0.f);
-    if (kind == PERMUTO_ACT_GELU) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));  // torch.nn.GELU()
+    if (kind == PERMUTO_ACT_GELU) return 0.5f * x * (1.0f + erf_fast(x * 0.70710678118654752f));  // torch.nn.GELU()
     return x;
 }
 
@@ -585,15 +595,27 @@ forward_mlp_kernel(const ForwardLinearArgs a) {
             const int width = ly.in_features;  // = out_features of layer i-1, a multiple of 16 up to HMAX
             ok = ring.drain() && ok;
             float h[HM];
+            const float* bias = a.layer[i - 1].bias;
+            const int kind = a.activation;
 #pragma unroll
             for (int c = 0; c < HM / 16; ++c) {
                 if (16 * c < width) {
                     float v[16];
                     tmem_load16(lane_base + col + 16u * c, v);
+                    if (bias) {  // 64-byte aligned groups of a tensor allocated by the caller: vector loads when possible
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        const float b = a.layer[i - 1].bias ? __ldg(a.layer[i - 1].bias + 16 * c + k) : 0.f;
-                        h[16 * c + k] = activate(v[k] + b, a.activation);
+                        for (int k = 0; k < 16; ++k) v[k] += __ldg(bias + 16 * c + k);
+                    }
+                    // one uniform branch per group, not one per element
+                    if (kind == PERMUTO_ACT_GELU) {
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) h[16 * c + k] = activate(v[k], PERMUTO_ACT_GELU);
+                    } else if (kind == PERMUTO_ACT_RELU) {
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) h[16 * c + k] = fmaxf(v[k], 0.f);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) h[16 * c + k] = v[k];
                     }
                 }
             }
