@@ -751,3 +751,76 @@ def test_remembered_static_inputs_follow_their_tensors(nat):
         run(table, torch.ones(c["nr_levels"] + 1, device=DEV))
     with pytest.raises(RuntimeError, match="lattice_values should be"):
         run(table[:, :-1].contiguous(), anneal)
+
+
+@pytest.mark.parametrize("feat", [4, 8])
+@pytest.mark.parametrize("d", [3, 4])
+def test_wider_features_reduce_to_the_reference_width(nat, feat, d):
+    """Pin for the widths the reference cannot run: the lattice geometry does not depend on the
+    feature width, so an F-wide table is F/2 two-feature tables that share slots.  The F-wide
+    kernels must therefore reproduce, column group by column group, what the two-feature path --
+    the one pinned to the reference -- gives on those tables, and, where the rebuilt reference
+    extension is present, what the reference itself gives on them."""
+    from oracle import ref_shim
+    L, cap, n = 8, 2 ** 16, 2 ** 17
+    gen = torch.Generator(device="cpu").manual_seed(100 * feat + d)
+    sig = np.geomspace(1.0, 1e-3, L)
+    wide = (torch.rand((L, cap, feat), generator=gen) * 2 - 1).to(DEV)
+    shift = (torch.randn((L, d), generator=gen) * 10).to(DEV)
+    pos = torch.rand((n, d), generator=gen).to(DEV)
+    go = torch.randn((n, feat * L), generator=gen).to(DEV)
+    dpg = torch.randn((n, d), generator=gen).to(DEV)
+    anneal = torch.ones(L, device=DEV)
+    enc_w = nat.EncodingWrapper.create(d, feat, nat.EncodingFixedParams(d, cap, L, feat, sig, shift, False, 1.0))
+    enc_2 = nat.EncodingWrapper.create(d, 2, nat.EncodingFixedParams(d, cap, L, 2, sig, shift, False, 1.0))
+    ref = ref_shim.RefEncoding(d, cap, L, sig, shift) if ref_shim.available() else None
+    Iw = nat.EncodingInput(wide, pos, anneal, True, True)
+    out_w = enc_w.forward(Iw)
+    tg_w, pg_w = enc_w.backward(Iw, go)
+    tg2_w, ggf_w = enc_w.double_backward_from_positions(Iw, dpg, go)
+    ga_w, _ = enc_w.backward(nat.EncodingInput(wide, pos, anneal, True, False), go.abs())   # sum|addend| per entry
+    cols = torch.arange(feat * L, device=DEV).view(L, feat)
+    pg_sum = torch.zeros_like(pg_w)
+    for h in range(feat // 2):
+        sub = wide[:, :, 2 * h:2 * h + 2].contiguous()
+        pick = cols[:, 2 * h:2 * h + 2].reshape(-1)               # columns of this pair in the wide rows
+        go_h, I2 = go[:, pick].contiguous(), nat.EncodingInput(sub, pos, anneal, True, True)
+        out_2 = enc_2.forward(I2)
+        assert torch.equal(out_w[:, pick], out_2)                  # same blend, same order: bit for bit
+        tg_2, pg_2 = enc_2.backward(I2, go_h)
+        bound = BWD_RTOL * ga_w[:, :, 2 * h:2 * h + 2] + 1e-6 * ga_w.amax()
+        assert torch.all((tg_w[:, :, 2 * h:2 * h + 2] - tg_2).abs() <= bound)
+        pg_sum += pg_2
+        tg2_2, ggf_2 = enc_2.double_backward_from_positions(I2, dpg, go_h)
+        lvl2 = tg2_2.abs().amax(dim=(1, 2), keepdim=True)
+        assert torch.all((tg2_w[:, :, 2 * h:2 * h + 2] - tg2_2).abs() <= BWD_RTOL * lvl2 + 1e-30)
+        assert torch.all((ggf_w[:, pick] - ggf_2).abs() <= BWD_RTOL * ggf_2.abs().max())
+        if ref is not None:
+            f_ref = ref.forward_raw(sub, pos, anneal).permute(2, 0, 1).reshape(n, -1)
+            assert torch.all((out_w[:, pick] - f_ref).abs() <= FWD_RTOL * f_ref.abs() + 1e-6 * f_ref.abs().max())
+            tg_ref, _ = ref.backward_raw(sub, pos, anneal, go_h.reshape(n, L, 2).permute(1, 2, 0).contiguous(), True, True)
+            assert torch.all((tg_w[:, :, 2 * h:2 * h + 2] - tg_ref).abs() <= 2 * bound)
+    assert torch.all((pg_w - pg_sum).abs() <= BWD_RTOL * pg_sum.abs().max())
+
+
+def test_half_precision_table_reduces_to_the_fp32_path(nat):
+    """Pin for fp16 storage: an fp16 entry converts to fp32 exactly, so gathering from the fp16
+    table must give BIT FOR BIT what the fp32 path -- the one pinned to the reference -- gives on
+    the same values held as fp32; and the live reference on those values agrees to rtol 1e-5."""
+    from oracle import ref_shim
+    d, L, cap, n = 3, 16, 2 ** 18, 2 ** 18
+    sig, table, shift, pos, go, dpg = _big(d, L, cap, n, 1e-3, 77)
+    table = (table * 1e4).half()
+    as_fp32 = table.float()
+    anneal = torch.ones(L, device=DEV)
+    enc = nat.EncodingWrapper.create(d, 2, nat.EncodingFixedParams(d, cap, L, 2, sig, shift, False, 1.0))
+    Ih, If = nat.EncodingInput(table, pos, anneal, True, True), nat.EncodingInput(as_fp32, pos, anneal, True, True)
+    out = enc.forward(Ih)
+    assert torch.equal(out, enc.forward(If))
+    assert torch.equal(enc.backward(nat.EncodingInput(table, pos, anneal, False, True), go)[1],
+                       enc.backward(nat.EncodingInput(as_fp32, pos, anneal, False, True), go)[1])
+    assert torch.equal(enc.double_backward_from_positions(Ih, dpg, go, need_lattice_grad=False)[1],
+                       enc.double_backward_from_positions(If, dpg, go, need_lattice_grad=False)[1])
+    if ref_shim.available():
+        f_ref = ref_shim.RefEncoding(d, cap, L, sig, shift).forward_raw(as_fp32, pos, anneal).permute(2, 0, 1).reshape(n, -1)
+        assert torch.all((out - f_ref).abs() <= FWD_RTOL * f_ref.abs() + 1e-6 * f_ref.abs().max())
