@@ -1064,10 +1064,10 @@ __global__ void __launch_bounds__(kThreads) debug_kernel(const DebugArgs a) {
 // re-reads the positions and touches only its own 32-byte pieces of every 128-byte line of the
 // feature rows, which costs a 4x DRAM over-fetch on the gradient reads with one step per sweep
 // -- but a larger set of table slices is live in L2 at once: capacity * 4F bytes per level for
-// the values and as much again for their gradient.  Measured on B200 (pos_dim 3 and 4,
+// the values and as much again for their gradient.  Measured on B200 (pos_dim 3, 4 and 6,
 // capacities 2^18..2^20, F = 2): scatter-only kernels are fastest with every level in one sweep
-// even when the gradient table exceeds L2; gather kernels want about 96 MB live, gather+scatter
-// kernels about 64 MB.
+// even when the gradient table exceeds L2; gather kernels with two sweeps, the finest third of
+// the levels in the second; gather+scatter kernels with about 64 MB live.
 enum class Traffic { Gather, Scatter, Both };
 
 inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t, int lps) {
@@ -1078,8 +1078,20 @@ inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t, int 
         const double mb = 1024.0 * 1024.0;
         if (t == Traffic::Scatter)
             lpp = levels;
-        else if (t == Traffic::Gather)
-            lpp = (int)(96.0 * mb / slice);
+        else if (t == Traffic::Gather) {
+            // Coarse levels touch few slots whatever the capacity; what must fit in L2 together
+            // is the saturated, fine levels of a pass.  Two passes with the finest third of the
+            // levels in the second one measured best from capacity 2^18 to 2^20 (forward at 2^20 and
+            // 24 levels: 0.70 ms against 0.91 with two equal passes and 0.93 with one); tables of a
+            // few MB stay in one pass, very large slices are capped at 128 MB per pass.
+            if (slice * levels <= 32.0 * mb) {
+                lpp = levels;
+            } else {
+                lpp = ((2 * levels + 2) / 3 + lps - 1) / lps * lps;
+                const int cap = (int)(128.0 * mb / slice);
+                if (lpp > cap) lpp = cap;
+            }
+        }
         else
             lpp = (int)(64.0 * mb / (slice + 4.0 * p.nr_feat * p.capacity));  // values + their fp32 gradient
     }
