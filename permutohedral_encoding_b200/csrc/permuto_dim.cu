@@ -1066,8 +1066,9 @@ __global__ void __launch_bounds__(kThreads) debug_kernel(const DebugArgs a) {
 // -- but a larger set of table slices is live in L2 at once: capacity * 4F bytes per level for
 // the values and as much again for their gradient.  Measured on B200 (pos_dim 3, 4 and 6,
 // capacities 2^18..2^20, F = 2): scatter-only kernels are fastest with every level in one sweep
-// even when the gradient table exceeds L2; gather kernels with two sweeps, the finest third of
-// the levels in the second; gather+scatter kernels with about 64 MB live.
+// up to a gradient table of about 100 MB; gather kernels, and scatter kernels beyond that, with
+// two sweeps, the finest third of the levels in the second; gather+scatter kernels with about
+// 64 MB live.
 enum class Traffic { Gather, Scatter, Both };
 
 inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t, int lps) {
@@ -1076,8 +1077,19 @@ inline int pick_levels_per_pass(const Problem& p, int requested, Traffic t, int 
     if (lpp <= 0) {
         const double slice = (p.table_half ? 2.0 : 4.0) * p.nr_feat * p.capacity;
         const double mb = 1024.0 * 1024.0;
-        if (t == Traffic::Scatter)
-            lpp = levels;
+        if (t == Traffic::Scatter) {
+            // one sweep while the fp32 gradient table is within reach of L2 (measured up to the
+            // 100.7 MB of capacity 2^19 x 24 levels); beyond that the same two sweeps as the gather
+            // kernels (capacity 2^20 x 24 levels, 201 MB: 1.05 ms against 1.84 in one sweep)
+            const double gslice = 4.0 * p.nr_feat * p.capacity;
+            if (gslice * levels <= 128.0 * mb) {
+                lpp = levels;
+            } else {
+                lpp = ((2 * levels + 2) / 3 + lps - 1) / lps * lps;
+                const int cap = (int)(128.0 * mb / gslice);
+                if (lpp > cap) lpp = cap;
+            }
+        }
         else if (t == Traffic::Gather) {
             // Coarse levels touch few slots whatever the capacity; what must fit in L2 together
             // is the saturated, fine levels of a pass.  Two passes with the finest third of the
