@@ -4,7 +4,8 @@
  * This is the boundary a binding of the reference project would target instead of its
  * pybind11 module `permutohedral_encoding_bindings._<cc>_C` (reference: src/PyBridge.cxx:13-45,
  * include/permutohedral_encoding/Encoding.cuh:14-188).  Plain pointers and sizes only: the
- * caller owns every buffer, the library allocates nothing, keeps no state between calls and
+ * caller owns every buffer, the library allocates nothing, keeps no state between calls (beyond
+ * the cached multiprocessor count of each device and the per-thread error message) and
  * never frees caller memory.  All device pointers must belong to the CUDA device that is
  * current on the calling thread; work is enqueued on `stream` (a cudaStream_t passed as
  * void*, NULL = the legacy default stream) and the functions return without synchronising.
